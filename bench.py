@@ -1,0 +1,293 @@
+#!/usr/bin/env python
+"""Benchmark of the MCTS-NC search hot path: playouts/s for Connect 4, acp_prodigal, 4 trees x 256 playouts,
+2000 search steps per root, 256 seeded random roots per pass.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" of the benchmark is one pass over the whole batch of roots (every root is searched for `--search-steps`
+MCTS steps).  With N > 1 (launched by torchrun, one rank per GPU) every rank grows 4 trees of every search with the
+random streams of a 4N-tree search, and the per-root-action sums are all-reduced over NCCL once per pass (root
+parallelism; per-GPU work is fixed: weak scaling).  Rank 0 prints one JSON line.
+
+`--impl reference` times the CPU restatement of the reference's kernels (oracle/) on the host cores, one root per
+thread, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+A = 7
+INST_PER_PLY = 65.0  # thread instructions of one playout ply in the bitboard formulation (yardstick)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--roots", type=int, default=256)
+    ap.add_argument("--search-steps", type=int, default=2000)
+    ap.add_argument("--trees", type=int, default=4)
+    ap.add_argument("--playouts", type=int, default=256)
+    ap.add_argument("--variant", default="acp_prodigal")
+    ap.add_argument("--max-plies", type=int, default=20)
+    ap.add_argument("--threads-per-tree", type=int, default=0)
+    ap.add_argument("--cpu-sample-roots", type=int, default=0, help="roots of the CPU baseline sample (0 = choose)")
+    ap.add_argument("--cpu-sample-steps", type=int, default=150)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "sm_max_mhz": float(p.get("sm_max_mhz", 1965.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_roots(args):
+    from mcts_numba_cuda_b200.roots import c4_random_roots
+    return c4_random_roots(args.roots, args.max_plies, seed=0)
+
+
+def oracle_search(job):
+    from oracle.oracle import OracleMCTSNC
+    board, fills, turn, trees, playouts, variant, steps = job
+    o = OracleMCTSNC((6, 7), 7, 7, n_trees=trees, n_playouts=playouts, variant=variant, seed=0,
+                     node_capacity=steps * A + 8)
+    t0 = time.perf_counter()
+    o.run(board, fills, int(turn), steps)
+    return o.playouts, o.plies, time.perf_counter() - t0
+
+
+def cpu_port_baseline(args, boards, fills, turns, threads, n_roots, steps):
+    """The oracle (CPU restatement of the reference's kernels) on `threads` host threads, one root per thread."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as om
+    om.lib()
+    jobs = [(boards[i % len(boards)], fills[i % len(boards)], turns[i % len(boards)], args.trees, args.playouts,
+             args.variant, steps) for i in range(n_roots)]
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        res = list(ex.map(oracle_search, jobs))
+    wall = time.perf_counter() - t0
+    playouts = sum(r[0] for r in res)
+    plies = sum(r[1] for r in res)
+    return playouts, plies, wall
+
+
+def config_dict(args, n_gpus):
+    return {"workload": f"Connect-4 6x7 {args.variant}, n_trees={args.trees} per GPU, n_playouts={args.playouts}, "
+                        f"search_steps={args.search_steps}, {args.roots} seeded random roots (0..{args.max_plies} plies) per pass",
+            "trees_per_search_total": args.trees * n_gpus, "parallelism": f"root-parallel x{n_gpus}" if n_gpus > 1 else "single GPU",
+            "l2": "no flush: the tree pools of one pass (~0.5 GB) exceed the 126 MB L2", "seed": 0, "ucb_c": 2.0}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    boards, fills, turns = make_roots(args)
+    cores = os.cpu_count() or 1
+    steps = args.cpu_sample_steps
+    n_roots = args.cpu_sample_roots or cores
+    times, total_playouts = [], 0
+    for i in range(args.warmup + args.steps):
+        playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, cores, n_roots, steps)
+        if i >= args.warmup:
+            times.append(wall)
+            total_playouts += playouts
+    value = total_playouts / sum(times)
+    sample = f"{n_roots} roots x {steps} search steps per pass, one root per thread"
+    print(json.dumps({"impl": "reference", "metric": "playouts/sec", "value": value, "unit": "playouts/s", "n_gpus": args.gpus,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
+                      "data": "synthetic", "config": config_dict(args, args.gpus),
+                      "cpu_baseline": {"value": value, "unit": "playouts/s", "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": value, "unit": "playouts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                      "gpu_launches": 0}))
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    import torch
+    import torch.distributed as dist
+    from mcts_numba_cuda_b200 import _abi
+    from mcts_numba_cuda_b200.distributed import RootParallelMCTSNC
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the search has no CPU path")
+    _abi.lib()  # fails loudly if the extension was not built
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    n_gpus = world
+    boards, fills, turns = make_roots(args)
+    B = args.roots
+    searcher = RootParallelMCTSNC((6, 7), 7, 7, n_trees=args.trees, n_playouts=args.playouts, variant=args.variant,
+                                  search_steps_limit=args.search_steps, max_batch=B, device=local_rank, rank=rank,
+                                  world_size=world, seed=0, ucb_c=2.0, threads_per_tree=args.threads_per_tree)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- device-resident passes (value, roofline)
+    searcher.search_async(boards, fills, turns, args.search_steps, reseed=True)  # stages the roots once
+    torch.cuda.synchronize()
+    for _ in range(max(args.warmup - 1, 0)):
+        searcher.search_async(None, None, None, args.search_steps, reseed=True)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for k in range(args.steps):
+        searcher.search_async(None, None, None, args.search_steps, reseed=True)
+        ev[k + 1].record()
+    barrier()
+    dev_ms = ev[0].elapsed_time(ev[-1])
+    res = searcher.fetch(B)
+    local_playouts = int(res["playouts"].sum())   # this rank's trees
+    local_plies = int(res["plies"].sum())
+    kernel_ms = float(res["device_ms"][0])         # search kernel of the last pass (CUDA events inside the library)
+    status = int(np.bitwise_or.reduce(res["status"]))
+    ub_draws = int(res["ub_draws"].sum())
+    # ---------------------------------------------------------------- end-to-end passes through the public API
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out = searcher.run_batch(boards, fills, turns, args.search_steps, reseed=True)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    # max over ranks of the timed regions, sums of the work
+    stats = torch.tensor([dev_ms, e2e_s * 1e3, kernel_ms], dtype=torch.float64, device="cuda")
+    work = torch.tensor([local_playouts, local_plies], dtype=torch.int64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    dev_ms, e2e_ms, kernel_ms = [float(x) for x in stats.tolist()]
+    playouts_per_pass, plies_per_pass = [int(x) for x in work.tolist()]
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    pk = peaks()
+    value = playouts_per_pass * args.steps / (dev_ms * 1e-3)
+    e2e_value = playouts_per_pass * args.steps / (e2e_ms * 1e-3)
+    thr, per_sm, sms, nbytes = (np.zeros(1, np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32), np.zeros(1, np.int64))
+    import ctypes
+    _abi.lib().mctsnc_query(searcher.local._handle, thr.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
+                            per_sm.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
+                            sms.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
+                            nbytes.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)))
+    sm_count = int(sms[0])
+    # dominant kernel: the search kernel.  Per rank and launch it plays plies_per_pass / n_gpus plies.
+    plies_per_launch = plies_per_pass / n_gpus
+    playouts_per_launch = playouts_per_pass / n_gpus
+    tree_steps_per_launch = B * args.trees * args.search_steps
+    # algorithmic HBM bytes: 32 B of stream state per playout, ~1.3 KB of tree records per tree-step
+    algo_bytes = 32.0 * playouts_per_launch + 1300.0 * tree_steps_per_launch
+    hbm_achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+    peak_inst = sm_count * 4 * 32 * pk["sm_max_mhz"] * 1e6
+    inst_achieved = plies_per_launch * INST_PER_PLY / (kernel_ms * 1e-3)
+    line = {
+        "metric": "playouts/sec", "value": value, "unit": "playouts/s", "n_gpus": n_gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int32", "data": "synthetic", "config": config_dict(args, n_gpus),
+        "e2e": {"value": e2e_value, "unit": "playouts/s", "h2d_bytes_per_step": int(B * 17),
+                "d2h_bytes_per_step": int(B * (3 * A * 8 + 2 * A + 80)), "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": args.steps * 4,
+        "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": hbm_achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "c4::search_kernel<false>", "kernel_ms": kernel_ms,
+                     "note": "the search is instruction-issue bound, not HBM bound: see issue_roofline"},
+        "issue_roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12,
+                           "unit": "T thread-inst/s", "frac": inst_achieved / peak_inst,
+                           "plies_per_playout": plies_per_launch / max(playouts_per_launch, 1),
+                           "inst_per_ply_yardstick": INST_PER_PLY, "sm_count": sm_count,
+                           "peak_clock_mhz": pk["sm_max_mhz"]},
+        "clocks": clocks, "threads_per_tree": int(thr[0]), "blocks_per_sm": int(per_sm[0]),
+        "device_bytes": int(nbytes[0]), "status_bits": status, "ub_draws_per_pass": ub_draws,
+        "playouts_per_pass": playouts_per_pass, "best_action_checksum": int(out["best_action"].astype(np.int64).sum()),
+    }
+    if n_gpus == 1 and not args.no_cpu_baseline:
+        steps = args.cpu_sample_steps
+        n_roots = args.cpu_sample_roots or 4
+        playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, 1, n_roots, steps)
+        line["cpu_baseline"] = {"value": playouts / wall, "unit": "playouts/s", "cores": 1, "kind": "port",
+                                "sample": f"{n_roots} roots x {steps} search steps, sequential, {wall:.1f} s"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

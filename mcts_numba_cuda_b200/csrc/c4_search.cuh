@@ -1,0 +1,591 @@
+// Connect-4 search kernel: the whole MCTS-NC loop of one tree in one thread block, all steps on the device.
+//
+// Replaces, per step, the reference kernels _select (src/mctsnc.py:1293-1365), _expand_1_* (:1368-1681),
+// _expand_2_* (:1691-1821), _playout_ocp / _playout_acp_* (:1824-2081), _backup_ocp / _backup_1_acp_* /
+// _backup_2_acp (:2084-2220), the _reset kernel (:1260-1290) and the Connect-4 device functions
+// (src/mctsnc_game_mechanics.py:89-179).
+//
+// Work split inside a block: warp 0 walks the tree (select), creates the children (expand) and writes the statistics
+// back (backup); all threads play the random games.  A thread keeps playing its own list of games back to back (one
+// per expanded child and playout index, the reference's thread (tree, action, t)), so the lanes of a warp wait for
+// each other once per step, not once per game.
+//
+// Position encoding: column c of the 6x7 board owns bits 7c .. 7c+5 (bit 7c = bottom cell) and a guard bit 7c+6 that
+// stays 0, so that shifts by 1, 6, 7, 8 test the four line directions without wrapping between columns.
+#pragma once
+#include "common.cuh"
+#include "rng.cuh"
+
+namespace mctsnc {
+namespace c4 {
+
+constexpr int ROWS = 6, COLS = 7, A = 7;
+constexpr unsigned long long BOTTOM_ROW = 0x0000040810204081ULL;  // bit 7c for c = 0..6
+constexpr unsigned long long TOP_ROW = BOTTOM_ROW << 5;
+constexpr unsigned long long FULL_BOARD = BOTTOM_ROW * 0x3FULL;
+
+__host__ __device__ __forceinline__ bool has_four(unsigned long long p) {
+    unsigned long long m, r;
+    m = p & (p >> 7);
+    r = m & (m >> 14);
+    m = p & (p >> 6);
+    r |= m & (m >> 12);
+    m = p & (p >> 8);
+    r |= m & (m >> 16);
+    m = p & (p >> 1);
+    r |= m & (m >> 2);
+    return r != 0;
+}
+
+// set of columns that still have room, from the occupancy bitboard
+__host__ __device__ __forceinline__ unsigned legal_columns(unsigned long long all) {
+    unsigned l = 0;
+#pragma unroll
+    for (int c = 0; c < COLS; c++) l |= ((all >> (7 * c + 5)) & 1ULL) ? 0u : (1u << c);
+    return l;
+}
+
+// among tied maxima the reference's stride-halving reduction keeps the left operand (src/mctsnc.py:1343-1351), which
+// over 8 slots ranks the actions 0,4,2,6,1,5,3 (smallest bit-reversed index wins)
+__device__ __forceinline__ int pick_among_tied(unsigned m) {
+    if (m & 1u) return 0;
+    if (m & 16u) return 4;
+    if (m & 4u) return 2;
+    if (m & 64u) return 6;
+    if (m & 2u) return 1;
+    if (m & 32u) return 5;
+    return 3;
+}
+
+__device__ __forceinline__ unsigned ordered_key(float v) {
+    unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Byte-for-byte emulation of one playout of the reference (src/mctsnc.py:2049-2069 with the Connect-4 functions of
+// src/mctsnc_game_mechanics.py:102-179) on int8 arrays.  Only entered when a uniform draw equals 1.0f, which makes
+// the reference read legal_actions_with_count[count]: a value left by an earlier ply of the same playout, or a slot
+// never written (read as 0 here).  numba wraps negative indices once; rows below 0 therefore address the board from
+// the bottom.  The playout is replayed from its first ply so that the stale slots hold what they would hold.
+struct EmuResult {
+    int outcome;
+    unsigned plies;
+    unsigned ub;
+};
+
+__device__ __forceinline__ int emu_cell(const signed char *board, int i, int j, unsigned &err) {
+    if (i < 0) i += ROWS;
+    if (j < 0) j += COLS;
+    if (i < 0 || i >= ROWS || j < 0 || j >= COLS) {
+        err = 1;
+        return 0;
+    }
+    return board[i * COLS + j];
+}
+
+__device__ __forceinline__ int emu_line(const signed char *board, int i, int j, int di, int dj, int token, unsigned &err) {
+    int total = 0;
+    for (int k = 1; k < 4; k++) {
+        int ii = i + k * di, jj = j + k * dj;
+        if ((di < 0 && ii < 0) || (di > 0 && ii >= ROWS) || (dj < 0 && jj < 0) || (dj > 0 && jj >= COLS)) break;
+        if (emu_cell(board, ii, jj, err) != token) break;
+        total++;
+    }
+    return total;
+}
+
+__device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsigned long long pos, int turn,
+                                                   unsigned long long &s0, unsigned long long &s1, unsigned &err) {
+    signed char board[ROWS * COLS];
+    signed char fills[COLS];
+    short legal[COLS + 1];
+    for (int j = 0; j < COLS; j++) {
+        int f = 0;
+        for (int h = 0; h < ROWS; h++) {
+            int bit = 7 * j + h;
+            int v = ((pos >> bit) & 1ULL) ? 1 : (((neg >> bit) & 1ULL) ? -1 : 0);
+            board[(ROWS - 1 - h) * COLS + j] = (signed char)v;
+            f += v != 0;
+        }
+        fills[j] = (signed char)f;
+    }
+    for (int j = 0; j <= COLS; j++) legal[j] = 0;
+    EmuResult r = {2, 0u, 0u};
+    for (;;) {
+        int count = 0;
+        for (int j = 0; j < COLS; j++)
+            if (fills[j] < ROWS) legal[count++] = (short)j;
+        float u = rng_uniform_f32(s0, s1);
+        int ord = (int)(short)__float2int_rz(__fmul_rn(u, (float)count));
+        if (u >= 1.0f) r.ub++;
+        if (ord < 0 || ord > COLS) {
+            err = 1;
+            ord = 0;
+        }
+        int a = legal[ord];
+        fills[a] += 1;
+        int row = ROWS - fills[a];
+        if (row < 0) row += ROWS;
+        if (row < 0) {
+            err = 1;
+            row = 0;
+        }
+        board[row * COLS + a] = (signed char)turn;
+        turn = -turn;
+        r.plies++;
+        // compute_outcome_c4(board, fills, turn, a)
+        int token = -turn;
+        int i = ROWS - fills[a];
+        int out = 2;
+        if (emu_line(board, i, a, -1, 0, token, err) + emu_line(board, i, a, 1, 0, token, err) >= 3) out = token;
+        else if (emu_line(board, i, a, 0, 1, token, err) + emu_line(board, i, a, 0, -1, token, err) >= 3) out = token;
+        else if (emu_line(board, i, a, -1, 1, token, err) + emu_line(board, i, a, 1, -1, token, err) >= 3) out = token;
+        else if (emu_line(board, i, a, -1, -1, token, err) + emu_line(board, i, a, 1, 1, token, err) >= 3) out = token;
+        else {
+            bool draw = true;
+            for (int j = 0; j < COLS; j++)
+                if (fills[j] < ROWS) draw = false;
+            if (draw) out = 0;
+        }
+        if (out != 2) {
+            r.outcome = out;
+            return r;
+        }
+        if (r.plies > 4096u) {  // cannot happen; keeps the loop bounded whatever the memory holds
+            err = 1;
+            r.outcome = 0;
+            return r;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+
+struct Shared {
+    int path[48];
+    int path_ns[48];
+    int path_wins[48];
+    unsigned long long child_neg[A];
+    unsigned long long child_pos[A];
+    int child_action[A];
+    int child_outcome[A];   // 2 = ongoing
+    unsigned child_legal[A]; // columns with room in the child's position
+    int tally[A][2];        // per expanded child: games won by -1, by +1
+    int active[A];          // children that need real playouts
+    int child_out[A][2];    // trees_playout_outcomes_children (persists over steps)
+    short ae[A + 2];        // trees_actions_expanded row (persists over steps)
+    unsigned lut[128];      // lut[set] packs, 3 bits each, the columns of `set` in ascending order
+    int n_active;
+    int n_exp;
+    int mode;
+    int first_child;
+    int exp_mask;
+    int selected;
+    int sel_meta;
+    int path_len;
+    int pick;               // OCP: index (among expanded children) of the child that is played out
+    int root_turn;
+    int size;
+    int out_neg, out_pos;
+    unsigned status;
+    unsigned long long plies;
+    unsigned long long ub;
+};
+
+// The random streams of the tree (ACP: 7*P, OCP: P states of 16 B) stay in dynamic shared memory for the whole launch:
+// they are read at the start of every game and written back at its end, by one thread each.
+template <bool OCP>
+__global__ void search_kernel(const SearchParams p) {
+    __shared__ Shared s;
+    extern __shared__ ulonglong2 s_rng[];
+    const int g = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int nt = blockDim.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int P = p.n_playouts;
+    int4 *rec = p.rec + (long long)g * p.cap;
+    ulonglong2 *board = p.board + (long long)g * p.cap;
+    int *parent = p.parent + (long long)g * p.cap;
+    TreeState *st = p.state + g;
+    const bool thrifty = (p.variant == 0 || p.variant == 2);
+
+    const int n_streams = OCP ? P : A * P;
+    ulonglong2 *g_rng = p.rng_playout + (long long)g * n_streams;
+    for (int i = tid; i < n_streams; i += nt) s_rng[i] = g_rng[i];
+    for (int i = tid; i < 128; i += nt) {
+        unsigned packed = 0;
+        int k = 0;
+        for (int c = 0; c < COLS; c++)
+            if (i & (1 << c)) packed |= (unsigned)c << (3 * k++);
+        s.lut[i] = packed;
+    }
+    if (tid == 0) {
+        const int b = g / p.n_trees;
+        if (p.first) {
+            const int turn = p.root_turn[b];
+            rec[0] = make_int4(0, 0, -1, make_meta(0, false, 2, turn, 0));
+            board[0] = p.root_board[b];
+            parent[0] = -1;
+            s.size = 1;
+            s.root_turn = turn;
+            s.status = 0;
+            s.plies = 0;
+            s.ub = 0;
+            s.selected = 0;
+            s.path_len = 1;
+        } else {
+            s.size = st->size;
+            s.root_turn = meta_turn(rec[0].w);
+            s.status = st->status;
+            s.plies = st->plies;
+            s.ub = st->ub_draws;
+            s.selected = st->selected;
+            s.path_len = st->path_len;
+        }
+        // the "last step" arrays of the reference live as long as the instance: a new search starts from what the
+        // previous one left in them (trees_actions_expanded keeps stale entries in the thrifty layout)
+        s.out_neg = st->out_neg;
+        s.out_pos = st->out_pos;
+        for (int a = 0; a < A; a++) {
+            s.child_out[a][0] = p.child_out[(g * A + a) * 2 + 0];
+            s.child_out[a][1] = p.child_out[(g * A + a) * 2 + 1];
+        }
+        for (int a = 0; a < A + 2; a++) s.ae[a] = p.actions_expanded[g * (A + 2) + a];
+    }
+    __syncthreads();
+
+    const double c_ucb = (double)p.ucb_c;
+    unsigned my_plies = 0, my_ub = 0, my_err = 0;
+
+    for (int step = 0; step < p.steps; step++) {
+        // =========================================================== select + expand (warp 0)
+        if (warp == 0) {
+            int node = 0;
+            int4 r = rec[0];
+            int depth = 0;
+            if (lane == 0) {
+                s.path[0] = 0;
+                s.path_ns[0] = r.x;
+                s.path_wins[0] = r.y;
+            }
+            while ((r.w & 0x7F) != 0 && depth < 46) {
+                const unsigned mask = r.w & 0x7F;
+                int child = -1;
+                int4 cr = make_int4(0, 0, -1, 0);
+                unsigned key = 0;
+                if (lane < A && ((mask >> lane) & 1u)) {
+                    child = r.z + __popc(mask & ((1u << lane) - 1u));
+                    cr = rec[child];
+                    float v;
+                    if (cr.x == 0) {
+                        v = __int_as_float(0x7f800000);
+                    } else {
+                        // src/mctsnc.py:1337 -- evaluated in float64 (numba promotes int32/float32 and log(int32) to
+                        // float64), fused multiply-add as NVVM contracts it, rounded once to float32
+                        const double q = (double)cr.y / (double)__int2float_rn(cr.x);
+                        const double e = sqrt(log((double)r.x) / (double)cr.x);
+                        v = __double2float_rn(fma(c_ucb, e, q));
+                    }
+                    key = ordered_key(v);
+                }
+                const unsigned best = __reduce_max_sync(0xFFFFFFFFu, key);
+                const unsigned tied = __ballot_sync(0xFFFFFFFFu, key == best && child >= 0) & 0x7Fu;
+                const int w = pick_among_tied(tied);
+                node = __shfl_sync(0xFFFFFFFFu, child, w);
+                r.x = __shfl_sync(0xFFFFFFFFu, cr.x, w);
+                r.y = __shfl_sync(0xFFFFFFFFu, cr.y, w);
+                r.z = __shfl_sync(0xFFFFFFFFu, cr.z, w);
+                r.w = __shfl_sync(0xFFFFFFFFu, cr.w, w);
+                depth++;
+                if (lane == 0) {
+                    s.path[depth] = node;
+                    s.path_ns[depth] = r.x;
+                    s.path_wins[depth] = r.y;
+                }
+            }
+            // ------------------------------------------------------- expand (_expand_1_* and _expand_2_*)
+            const int sel_turn = meta_turn(r.w);
+            const int sel_depth = meta_depth(r.w);
+            int mode, n_exp = 0, exp_mask = 0, first_child = -1;
+            if (r.w & META_TERMINAL) {
+                mode = MODE_TERMINAL;
+                if (lane == 0) {
+                    const int o = meta_outcome(r.w);
+                    s.out_neg = o == -1 ? P : 0;
+                    s.out_pos = o == 1 ? P : 0;
+                    s.n_active = 0;
+                }
+            } else {
+                const ulonglong2 bb = board[node];  // x: stones of -1, y: stones of +1
+                const unsigned long long all = bb.x | bb.y;
+                const unsigned legal = legal_columns(all);
+                const int n_legal = __popc(legal);
+                long long room = p.node_limit - (long long)s.size;
+                if (room < 0) room = 0;
+                n_exp = n_legal < room ? n_legal : (int)room;
+                exp_mask = (int)legal;
+                for (int drop = n_legal - n_exp; drop > 0; drop--)  // keep the n_exp lowest legal actions
+                    exp_mask &= ~(1 << (31 - __clz(exp_mask)));
+                if (n_exp < n_legal && lane == 0) s.status |= STATUS_TREE_FULL;
+                if (n_exp > 0) {
+                    mode = MODE_ALL_CHILDREN;
+                    first_child = s.size;
+                    if (lane < A && ((exp_mask >> lane) & 1)) {
+                        const int k = __popc(exp_mask & ((1 << lane) - 1));
+                        const unsigned long long move = (all + (1ULL << (7 * lane))) & (0x3FULL << (7 * lane));
+                        unsigned long long cneg = bb.x, cpos = bb.y;
+                        if (sel_turn > 0) cpos |= move;
+                        else cneg |= move;
+                        const bool win = has_four(sel_turn > 0 ? cpos : cneg);
+                        const bool full = (all | move) == FULL_BOARD;
+                        const int outcome = win ? sel_turn : (full ? 0 : 2);
+                        board[first_child + k] = make_ulonglong2(cneg, cpos);
+                        parent[first_child + k] = node;
+                        s.child_neg[k] = cneg;
+                        s.child_pos[k] = cpos;
+                        s.child_action[k] = lane;
+                        s.child_outcome[k] = outcome;
+                        s.child_legal[k] = legal_columns(all | move);
+                        s.tally[k][0] = outcome == -1 ? P : 0;
+                        s.tally[k][1] = outcome == 1 ? P : 0;
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        s.size += n_exp;
+                        int pick = 0;
+                        if (OCP) {
+                            // src/mctsnc.py:1435 / :1511 -- float32 * int64 is a float64 product, truncated
+                            ulonglong2 es = p.rng_expand[g];
+                            const float u = rng_uniform_f32(es.x, es.y);
+                            p.rng_expand[g] = es;
+                            pick = __double2int_rz((double)u * (double)n_exp);
+                            if (pick >= n_exp) {  // u == 1.0f: undefined in the reference, clamped
+                                pick = n_exp - 1;
+                                s.ub++;
+                                s.status |= STATUS_UB_DRAW;
+                            }
+                            s.pick = pick;
+                        }
+                        int na = 0;
+                        for (int k = 0; k < n_exp; k++) {
+                            if (OCP && k != pick) {
+                                s.tally[k][0] = 0;
+                                s.tally[k][1] = 0;
+                                continue;
+                            }
+                            if (s.child_outcome[k] == 2) s.active[na++] = k;
+                        }
+                        s.n_active = na;
+                    }
+                } else {
+                    // no room for a single child: the selected node itself is played out
+                    mode = MODE_TREE_FULL;
+                    if (lane == 0) {
+                        s.child_neg[0] = bb.x;
+                        s.child_pos[0] = bb.y;
+                        s.child_action[0] = 0;
+                        s.child_outcome[0] = 2;
+                        s.child_legal[0] = legal;
+                        s.tally[0][0] = 0;
+                        s.tally[0][1] = 0;
+                        s.active[0] = 0;
+                        s.n_active = 1;
+                        s.pick = 0;
+                    }
+                }
+            }
+            // trees_actions_expanded in the layout of the variant (src/mctsnc.py:1430-1454, :1509-1531, :1583-1604,
+            // :1656-1681)
+            if (lane < A) {
+                if (thrifty) {
+                    if (mode == MODE_ALL_CHILDREN && ((exp_mask >> lane) & 1))
+                        s.ae[__popc(exp_mask & ((1 << lane) - 1))] = (short)lane;
+                } else {
+                    if (mode == MODE_ALL_CHILDREN) s.ae[lane] = ((exp_mask >> lane) & 1) ? (short)lane : (short)-1;
+                    else s.ae[lane] = -1;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                s.ae[A + 1] = (short)(mode == MODE_ALL_CHILDREN ? n_exp : 1);
+                int m2 = mode;
+                if (OCP && mode == MODE_ALL_CHILDREN) m2 = thrifty ? s.pick : s.child_action[s.pick];
+                s.ae[A] = (short)m2;
+                if (!OCP && mode != MODE_ALL_CHILDREN) s.ae[0] = 0;
+                s.mode = mode;
+                s.n_exp = n_exp;
+                s.exp_mask = exp_mask;
+                s.first_child = first_child;
+                s.selected = node;
+                s.sel_meta = r.w;
+                s.path_len = depth + 1;
+            }
+            (void)sel_depth;
+        }
+        __syncthreads();
+
+        // =========================================================== playouts (all threads)
+        {
+            const int n_items = s.n_active << p.log2_playouts;
+            const int child_turn = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
+            int item = tid;
+            bool running = item < n_items;
+            // state of the game in flight
+            unsigned long long cur = 0, all = 0, s0 = 0, s1 = 0;
+            unsigned legal = 0;
+            int cnt = 0, turn = 0, k = 0;
+            unsigned plies_at_start = 0;
+            int rng_idx = 0;
+            bool fresh = true;
+            while (running) {
+                if (fresh) {
+                    k = s.active[item >> p.log2_playouts];
+                    const int t = item & (P - 1);
+                    // src/mctsnc.py:1938 / :2028 (ACP: stream (tree, action, t)), cuda.grid(1) at :1849 (OCP: (tree, t))
+                    rng_idx = OCP ? t : s.child_action[k] * P + t;
+                    const ulonglong2 rs = s_rng[rng_idx];
+                    s0 = rs.x;
+                    s1 = rs.y;
+                    const unsigned long long cneg = s.child_neg[k], cpos = s.child_pos[k];
+                    turn = child_turn;
+                    all = cneg | cpos;
+                    cur = turn > 0 ? cpos : cneg;
+                    legal = s.child_legal[k];
+                    cnt = __popc(legal);
+                    plies_at_start = my_plies;
+                    fresh = false;
+                }
+                // ---- one ply (src/mctsnc.py:2059-2064, :2069)
+                const float u = rng_uniform_f32(s0, s1);
+                const int ord = __float2int_rz(__fmul_rn(u, (float)cnt));
+                int outcome = 2;
+                if (ord >= cnt) {
+                    // u == 1.0f: replay this game through the byte-level emulation of the reference
+                    const ulonglong2 rs = s_rng[rng_idx];
+                    s0 = rs.x;
+                    s1 = rs.y;
+                    const EmuResult er = playout_emulated(s.child_neg[k], s.child_pos[k], child_turn, s0, s1, my_err);
+                    outcome = er.outcome;
+                    my_plies = plies_at_start + er.plies;  // the abandoned attempt is not counted twice
+                    my_ub += er.ub;
+                } else {
+                    const int col = (s.lut[legal] >> (3 * ord)) & 7;
+                    const unsigned long long nall = all | (all + (1ULL << (7 * col)));
+                    const unsigned long long mine = cur | (nall ^ all);
+                    cur = all ^ cur;
+                    all = nall;
+                    my_plies++;
+                    if (has_four(mine)) {
+                        outcome = turn;
+                    } else {
+                        if ((all >> (7 * col + 5)) & 1ULL) {
+                            legal &= ~(1u << col);
+                            cnt--;
+                        }
+                        if (cnt == 0) outcome = 0;
+                    }
+                    turn = -turn;
+                }
+                if (outcome != 2) {
+                    s_rng[rng_idx] = make_ulonglong2(s0, s1);
+                    if (outcome < 0) atomicAdd(&s.tally[k][0], 1);
+                    else if (outcome > 0) atomicAdd(&s.tally[k][1], 1);
+                    item += nt;
+                    running = item < n_items;
+                    fresh = true;
+                }
+            }
+        }
+        __syncthreads();
+
+        // =========================================================== backup (warp 0)
+        if (warp == 0) {
+            const int mode = s.mode;
+            const int n_exp = s.n_exp;
+            const int sel_meta = s.sel_meta;
+            const int child_turn = -meta_turn(sel_meta);
+            int neg_tot = 0, pos_tot = 0;
+            long long n_tot = P;
+            if (mode == MODE_ALL_CHILDREN) {
+                int my_neg = 0, my_pos = 0;
+                if (lane < n_exp) {
+                    my_neg = s.tally[lane][0];
+                    my_pos = s.tally[lane][1];
+                    const bool played = !OCP || lane == s.pick;
+                    const int o = s.child_outcome[lane];
+                    // children start from ns = ns_wins = 0 (src/mctsnc.py:1819-1820), then _backup_1_acp_* / the
+                    // thread-0 part of _backup_ocp credit them (:2172-2177, :2104-2114)
+                    const int cns = played ? P : 0;
+                    const int cw = played ? (child_turn == 1 ? my_neg : my_pos) : 0;
+                    rec[s.first_child + lane] =
+                        make_int4(cns, cw, -1, make_meta(0, o != 2, o, child_turn, meta_depth(sel_meta) + 1));
+                    if (!OCP) {
+                        s.child_out[s.child_action[lane]][0] = my_neg;
+                        s.child_out[s.child_action[lane]][1] = my_pos;
+                    }
+                }
+                neg_tot = __reduce_add_sync(0xFFFFFFFFu, my_neg);
+                pos_tot = __reduce_add_sync(0xFFFFFFFFu, my_pos);
+                if (!OCP) n_tot = (long long)P * n_exp;
+            } else if (mode == MODE_TERMINAL) {
+                neg_tot = s.out_neg;
+                pos_tot = s.out_pos;
+            } else {
+                neg_tot = s.tally[0][0];
+                pos_tot = s.tally[0][1];
+                if (!OCP && lane == 0) {
+                    s.child_out[0][0] = neg_tot;
+                    s.child_out[0][1] = pos_tot;
+                }
+            }
+            const int plen = s.path_len;
+            for (int e = lane; e < plen; e += 32) {
+                const int node = s.path[e];
+                const int turn_e = (e & 1) ? -s.root_turn : s.root_turn;
+                const int ns = s.path_ns[e] + (int)n_tot;
+                const int wins = s.path_wins[e] + (turn_e == 1 ? neg_tot : pos_tot);
+                if (e == plen - 1 && mode == MODE_ALL_CHILDREN) {
+                    rec[node] = make_int4(ns, wins, s.first_child, sel_meta | s.exp_mask);
+                } else {
+                    *reinterpret_cast<int2 *>(&rec[node]) = make_int2(ns, wins);
+                }
+            }
+            if (lane == 0) {
+                s.out_neg = neg_tot;
+                s.out_pos = pos_tot;
+            }
+            __syncwarp();
+        }
+    }
+
+    // =============================================================== leave the per-tree state for the next launch
+    if (my_plies) atomicAdd(&s.plies, (unsigned long long)my_plies);
+    if (my_ub) {
+        atomicAdd(&s.ub, (unsigned long long)my_ub);
+        atomicOr(&s.status, STATUS_UB_DRAW);
+    }
+    if (my_err) atomicOr(&s.status, STATUS_INTERNAL);
+    __syncthreads();
+    for (int i = tid; i < n_streams; i += nt) g_rng[i] = s_rng[i];
+    if (tid == 0) {
+        st->size = s.size;
+        st->selected = s.selected;
+        st->path_len = s.path_len;
+        st->out_neg = s.out_neg;
+        st->out_pos = s.out_pos;
+        st->status = s.status;
+        st->plies = s.plies;
+        st->ub_draws = s.ub;
+        for (int a = 0; a < A; a++) {
+            p.child_out[(g * A + a) * 2 + 0] = s.child_out[a][0];
+            p.child_out[(g * A + a) * 2 + 1] = s.child_out[a][1];
+        }
+        for (int a = 0; a < A + 2; a++) p.actions_expanded[g * (A + 2) + a] = s.ae[a];
+        for (int e = 0; e < s.path_len; e++) p.paths[g * PATH_CAP + e] = s.path[e];
+    }
+}
+
+}  // namespace c4
+}  // namespace mctsnc

@@ -1,0 +1,846 @@
+// Host side of libmctsnc_b200.so: the C ABI declared in include/mctsnc_b200.h, the handle that owns the device
+// memory of a searcher, the random-stream set-up, the two reduction kernels and the export of trees in the
+// reference's array formats.
+#include "../../include/mctsnc_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "c4_search.cuh"
+#include "common.cuh"
+#include "rng.cuh"
+
+using namespace mctsnc;
+
+namespace {
+
+constexpr int MAX_TREE_DEPTH = 2048;  // src/mctsnc.py:197
+
+#define CUDA_TRY(expr)                        \
+    do {                                      \
+        cudaError_t _e = (expr);              \
+        if (_e != cudaSuccess) return (int)_e; \
+    } while (0)
+
+int pow2ceil(int x) {
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+// device-side result block of one search, filled by the two reduction kernels
+struct DevResult {
+    int best_action;
+    int best_win_flag;
+    long long best_n;
+    long long best_n_wins;
+    long long playouts;
+    long long plies;
+    long long ub_draws;
+    unsigned status;
+    int n_root_actions;
+    int max_depth;
+    int max_size;
+    long long total_nodes;
+    long long depth_sum;
+};
+
+}  // namespace
+
+struct mctsnc_handle {
+    mctsnc_config cfg;
+    int A = 0;
+    int tpb_e1 = 0;
+    int tpb_roa = 0;
+    int sm_count = 0;
+    int threads = 0;
+    int blocks_per_sm = 0;
+    long long bytes = 0;
+    long long n_trees_total = 0;  // max_batch * n_trees
+    long long rng_per_search = 0; // playout streams per search of this handle
+    // device memory
+    int4 *rec = nullptr;
+    ulonglong2 *board = nullptr;
+    int *parent = nullptr;
+    TreeState *state = nullptr;
+    int *paths = nullptr;
+    short *actions_expanded = nullptr;
+    int *child_out = nullptr;
+    ulonglong2 *rng_playout = nullptr;
+    ulonglong2 *rng_expand = nullptr;
+    ulonglong2 *rng_playout_base = nullptr;
+    ulonglong2 *rng_expand_base = nullptr;
+    ulonglong2 *root_board = nullptr;
+    signed char *root_turn = nullptr;
+    long long *sums = nullptr;            // [max_batch][3A]
+    unsigned char *flags = nullptr;       // [max_batch][2A]: win flags, expanded-at-root
+    DevResult *dres = nullptr;            // [max_batch]
+    // pinned host staging
+    ulonglong2 *h_root_board = nullptr;
+    signed char *h_root_turn = nullptr;
+    long long *h_sums = nullptr;
+    unsigned char *h_flags = nullptr;
+    DevResult *h_dres = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+    long long last_steps = 0;
+    int staged_roots = 0;  // roots resident on the device from the last staging
+    size_t dyn_smem = 0;   // dynamic shared memory of the search kernel: the tree's random streams
+};
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------------------
+// kernels outside the search loop
+
+// copies the freshly seeded streams of one search into the slots of `batch` searches
+__global__ void replicate_streams_kernel(ulonglong2 *dst, const ulonglong2 *base, long long per_search, int batch) {
+    const long long n = per_search * batch;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = base[i % per_search];
+}
+
+// _reduce_over_trees_* (src/mctsnc.py:2223-2296): per root action the sums over the trees of a search of the root
+// visit count, the child's visit count and the child's win count; win flag from tree 0.  One block per search.
+// Also gathers the statistics behind performance_info (:448-494).
+__global__ void reduce_over_trees_kernel(const int4 *rec, const TreeState *state, long long cap, int n_trees, int A,
+                                         long long *sums, unsigned char *flags, DevResult *dres) {
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int4 *r0 = rec + (long long)b * n_trees * cap;
+    const int root_meta0 = r0[0].w;
+    const int root_turn = meta_turn(root_meta0);
+    const unsigned mask0 = root_meta0 & 0x7F;
+    for (int a = tid; a < A; a += blockDim.x) {
+        long long s_root = 0, s_n = 0, s_w = 0;
+        unsigned char win = 0;
+        const bool expanded = (mask0 >> a) & 1u;
+        if (expanded) {
+            for (int t = 0; t < n_trees; t++) {
+                const int4 *rt = r0 + (long long)t * cap;
+                const int4 root = rt[0];
+                s_root += root.x;
+                const unsigned mk = root.w & 0x7F;
+                if ((mk >> a) & 1u) {
+                    const int4 c = rt[root.z + __popc(mk & ((1u << a) - 1u))];
+                    s_n += c.x;
+                    s_w += c.y;
+                    if (t == 0) win = (c.w & META_TERMINAL) && meta_outcome(c.w) == root_turn;
+                }
+            }
+        }
+        sums[(long long)b * 3 * A + a] = s_root;
+        sums[(long long)b * 3 * A + A + a] = s_n;
+        sums[(long long)b * 3 * A + 2 * A + a] = s_w;
+        flags[(long long)b * 2 * A + a] = win;
+        flags[(long long)b * 2 * A + A + a] = expanded;
+    }
+    // statistics
+    __shared__ long long sh_depth[256];
+    __shared__ int sh_maxd[256];
+    long long dsum = 0;
+    int dmax = 0;
+    for (int t = 0; t < n_trees; t++) {
+        const int size = state[b * n_trees + t].size;
+        const int4 *rt = r0 + (long long)t * cap;
+        for (int i = tid; i < size; i += blockDim.x) {
+            const int d = meta_depth(rt[i].w);
+            dsum += d;
+            dmax = d > dmax ? d : dmax;
+        }
+    }
+    sh_depth[tid] = dsum;
+    sh_maxd[tid] = dmax;
+    __syncthreads();
+    for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+        if (tid < s) {
+            sh_depth[tid] += sh_depth[tid + s];
+            sh_maxd[tid] = max(sh_maxd[tid], sh_maxd[tid + s]);
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        DevResult d;
+        d.best_action = -1;
+        d.best_win_flag = 0;
+        d.best_n = 0;
+        d.best_n_wins = 0;
+        d.playouts = 0;
+        d.plies = 0;
+        d.ub_draws = 0;
+        d.status = 0;
+        d.max_size = 0;
+        d.total_nodes = 0;
+        for (int t = 0; t < n_trees; t++) {
+            const TreeState &ts = state[b * n_trees + t];
+            d.playouts += r0[(long long)t * cap].x;
+            d.plies += (long long)ts.plies;
+            d.ub_draws += (long long)ts.ub_draws;
+            d.status |= ts.status;
+            d.total_nodes += ts.size;
+            d.max_size = ts.size > d.max_size ? ts.size : d.max_size;
+        }
+        d.n_root_actions = __popc(mask0);
+        d.max_depth = sh_maxd[0];
+        d.depth_sum = sh_depth[0];
+        dres[b] = d;
+    }
+}
+
+// _reduce_over_actions_* (src/mctsnc.py:2299-2375): lexicographic max/argmax over (win_flag, n, n_wins) with the
+// reference's stride-halving reduction, which keeps the left operand on ties.  The thrifty variants reduce over
+// ordinals among the root's expanded actions, the prodigal ones over action indices.  One block of `width` threads
+// per search (width = tpb_roa).
+__global__ void reduce_over_actions_kernel(const long long *sums, const unsigned char *flags, int A, int width, int thrifty,
+                                           DevResult *dres) {
+    __shared__ short s_a[512];
+    __shared__ unsigned char s_f[512];
+    __shared__ long long s_n[512];
+    __shared__ long long s_w[512];
+    __shared__ short s_ord2act[512];
+    __shared__ int s_cnt;
+    const int b = blockIdx.x;
+    const int t = threadIdx.x;
+    const long long *sm = sums + (long long)b * 3 * A;
+    const unsigned char *fl = flags + (long long)b * 2 * A;
+    if (t == 0) {
+        int c = 0;
+        for (int a = 0; a < A; a++)
+            if (fl[A + a]) s_ord2act[c++] = (short)a;
+        s_cnt = c;
+    }
+    __syncthreads();
+    const int limit = thrifty ? s_cnt : A;
+    const int src = thrifty ? (t < limit ? s_ord2act[t] : 0) : t;
+    s_a[t] = (short)t;
+    if (t < limit) {
+        s_f[t] = fl[src];
+        s_n[t] = sm[A + src];
+        s_w[t] = sm[2 * A + src];
+    } else {
+        s_f[t] = 0;
+        s_n[t] = 0;
+        s_w[t] = 0;
+    }
+    __syncthreads();
+    for (int stride = width >> 1; stride > 0; stride >>= 1) {
+        if (t < stride) {
+            const int o = t + stride;
+            if ((s_f[t] < s_f[o]) || (s_f[t] == s_f[o] && s_n[t] < s_n[o]) ||
+                (s_f[t] == s_f[o] && s_n[t] == s_n[o] && s_w[t] < s_w[o])) {
+                s_a[t] = s_a[o];
+                s_f[t] = s_f[o];
+                s_n[t] = s_n[o];
+                s_w[t] = s_w[o];
+            }
+        }
+        __syncthreads();
+    }
+    if (t == 0) {
+        int best = s_a[0];
+        if (thrifty) best = best < s_cnt ? s_ord2act[best] : 0;
+        dres[b].best_action = best;
+        dres[b].best_win_flag = s_f[0];
+        dres[b].best_n = s_n[0];
+        dres[b].best_n_wins = s_w[0];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host helpers
+
+// create_xoroshiro128p_states(n, seed) restricted to the streams [first, first + count) with stride `stride`
+// between wanted streams (stream i is stream i-1 jumped 2^64 steps ahead)
+void make_streams(uint64_t seed, long long first, long long count, long long stride, ulonglong2 *out) {
+    RngState s;
+    rng_seed(s, seed);
+    long long idx = 0;
+    for (long long k = 0; k < count; k++) {
+        const long long want = first + k * stride;
+        while (idx < want) {
+            rng_jump(s);
+            idx++;
+        }
+        out[k].x = s.s0;
+        out[k].y = s.s1;
+    }
+}
+
+bool is_ocp(const mctsnc_config &c) { return c.variant == MCTSNC_OCP_THRIFTY || c.variant == MCTSNC_OCP_PRODIGAL; }
+bool is_thrifty(const mctsnc_config &c) { return c.variant == MCTSNC_OCP_THRIFTY || c.variant == MCTSNC_ACP_THRIFTY; }
+
+// int8 board + column fills -> bitboards; rejects positions the bitboard mechanics cannot represent
+int c4_encode_root(const int8_t *board, const int8_t *fills, ulonglong2 *out) {
+    unsigned long long neg = 0, pos = 0;
+    for (int j = 0; j < c4::COLS; j++) {
+        int f = 0;
+        bool gap = false;
+        for (int h = 0; h < c4::ROWS; h++) {
+            const int v = board[(c4::ROWS - 1 - h) * c4::COLS + j];
+            if (v == 0) {
+                gap = true;
+                continue;
+            }
+            if (gap || (v != 1 && v != -1)) return MCTSNC_E_BAD_ROOT;  // a disc above an empty cell
+            if (v > 0) pos |= 1ULL << (7 * j + h);
+            else neg |= 1ULL << (7 * j + h);
+            f++;
+        }
+        if (fills && fills[j] != f) return MCTSNC_E_BAD_ROOT;
+    }
+    if (c4::has_four(neg) || c4::has_four(pos)) return MCTSNC_E_BAD_ROOT;  // the game is over already
+    out->x = neg;
+    out->y = pos;
+    return 0;
+}
+
+template <typename T>
+int dev_alloc(mctsnc_handle *h, T **p, long long n) {
+    if (n <= 0) n = 1;
+    cudaError_t e = cudaMalloc((void **)p, (size_t)n * sizeof(T));
+    if (e != cudaSuccess) {
+        *p = nullptr;
+        cudaGetLastError();
+        return e == cudaErrorMemoryAllocation ? MCTSNC_E_NO_MEMORY : (int)e;
+    }
+    h->bytes += n * (long long)sizeof(T);
+    return 0;
+}
+
+void release(mctsnc_handle *h) {
+    cudaFree(h->rec);
+    cudaFree(h->board);
+    cudaFree(h->parent);
+    cudaFree(h->state);
+    cudaFree(h->paths);
+    cudaFree(h->actions_expanded);
+    cudaFree(h->child_out);
+    cudaFree(h->rng_playout);
+    cudaFree(h->rng_expand);
+    cudaFree(h->rng_playout_base);
+    cudaFree(h->rng_expand_base);
+    cudaFree(h->root_board);
+    cudaFree(h->root_turn);
+    cudaFree(h->sums);
+    cudaFree(h->flags);
+    cudaFree(h->dres);
+    cudaFreeHost(h->h_root_board);
+    cudaFreeHost(h->h_root_turn);
+    cudaFreeHost(h->h_sums);
+    cudaFreeHost(h->h_flags);
+    cudaFreeHost(h->h_dres);
+    if (h->ev0) cudaEventDestroy(h->ev0);
+    if (h->ev1) cudaEventDestroy(h->ev1);
+}
+
+const void *search_kernel_ptr(const mctsnc_config &c) {
+    return is_ocp(c) ? (const void *)c4::search_kernel<true> : (const void *)c4::search_kernel<false>;
+}
+
+// threads of the block that grows one tree: the largest of 256/128/64 for which `trees` blocks are resident at once,
+// so that a batch runs as one wave; 256 when even 64 does not fit
+int choose_threads(mctsnc_handle *h, long long trees) {
+    const int candidates[3] = {256, 128, 64};
+    for (int i = 0; i < 3; i++) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, search_kernel_ptr(h->cfg), candidates[i], h->dyn_smem) != cudaSuccess)
+            continue;
+        if ((long long)per_sm * h->sm_count >= trees) {
+            h->blocks_per_sm = per_sm;
+            return candidates[i];
+        }
+    }
+    int per_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, search_kernel_ptr(h->cfg), 256, h->dyn_smem);
+    h->blocks_per_sm = per_sm;
+    return 256;
+}
+
+int seed_streams(mctsnc_handle *h, int batch, cudaStream_t stream) {
+    const int grid = 148 * 4;
+    replicate_streams_kernel<<<grid, 256, 0, stream>>>(h->rng_playout, h->rng_playout_base, h->rng_per_search, batch);
+    if (is_ocp(h->cfg))
+        replicate_streams_kernel<<<grid, 256, 0, stream>>>(h->rng_expand, h->rng_expand_base, h->cfg.n_trees, batch);
+    return (int)cudaGetLastError();
+}
+
+int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t *extras, const int8_t *turns,
+                cudaStream_t stream) {
+    const int cells = h->cfg.board_rows * h->cfg.board_cols;
+    const int extra = h->cfg.extra_info_memory;
+    for (int b = 0; b < batch; b++) {
+        if (turns[b] != 1 && turns[b] != -1) return MCTSNC_E_BAD_ARGUMENT;
+        const int rc = c4_encode_root(boards + (long long)b * cells, extras ? extras + (long long)b * extra : nullptr,
+                                      &h->h_root_board[b]);
+        if (rc) return rc;
+        h->h_root_turn[b] = turns[b];
+    }
+    CUDA_TRY(cudaMemcpyAsync(h->root_board, h->h_root_board, sizeof(ulonglong2) * batch, cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaMemcpyAsync(h->root_turn, h->h_root_turn, batch, cudaMemcpyHostToDevice, stream));
+    return 0;
+}
+
+int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_t stream) {
+    SearchParams p;
+    p.rec = h->rec;
+    p.board = h->board;
+    p.parent = h->parent;
+    p.state = h->state;
+    p.paths = h->paths;
+    p.actions_expanded = h->actions_expanded;
+    p.child_out = h->child_out;
+    p.rng_playout = h->rng_playout;
+    p.rng_expand = h->rng_expand;
+    p.root_board = h->root_board;
+    p.root_turn = h->root_turn;
+    p.cap = h->cfg.node_capacity;
+    p.node_limit = h->cfg.max_tree_size < h->cfg.node_capacity ? h->cfg.max_tree_size : h->cfg.node_capacity;
+    p.n_trees = h->cfg.n_trees;
+    p.n_playouts = h->cfg.n_playouts;
+    p.log2_playouts = 0;
+    while ((1 << p.log2_playouts) < h->cfg.n_playouts) p.log2_playouts++;
+    p.n_actions = h->A;
+    p.variant = h->cfg.variant;
+    p.steps = steps;
+    p.first = first;
+    p.ucb_c = h->cfg.ucb_c;
+    const long long trees = (long long)batch * h->cfg.n_trees;
+    const int threads = h->cfg.threads_per_tree > 0 ? h->cfg.threads_per_tree : choose_threads(h, trees);
+    h->threads = threads;
+    if (is_ocp(h->cfg)) c4::search_kernel<true><<<(unsigned)trees, threads, h->dyn_smem, stream>>>(p);
+    else c4::search_kernel<false><<<(unsigned)trees, threads, h->dyn_smem, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+int launch_reduce_trees(mctsnc_handle *h, int batch, long long *sums, cudaStream_t stream) {
+    reduce_over_trees_kernel<<<batch, 256, 0, stream>>>(h->rec, h->state, h->cfg.node_capacity, h->cfg.n_trees, h->A, sums,
+                                                        h->flags, h->dres);
+    return (int)cudaGetLastError();
+}
+
+int launch_reduce_actions(mctsnc_handle *h, int batch, const long long *sums, cudaStream_t stream) {
+    reduce_over_actions_kernel<<<batch, h->tpb_roa, 0, stream>>>(sums, h->flags, h->A, h->tpb_roa, is_thrifty(h->cfg) ? 1 : 0,
+                                                                 h->dres);
+    return (int)cudaGetLastError();
+}
+
+int fetch_results(mctsnc_handle *h, int batch, const long long *sums_dev, mctsnc_result *results, cudaStream_t stream) {
+    const int A = h->A;
+    CUDA_TRY(cudaMemcpyAsync(h->h_sums, sums_dev, sizeof(long long) * 3 * A * batch, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaMemcpyAsync(h->h_flags, h->flags, (size_t)2 * A * batch, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaMemcpyAsync(h->h_dres, h->dres, sizeof(DevResult) * batch, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    for (int b = 0; b < batch; b++) {
+        mctsnc_result &r = results[b];
+        const DevResult &d = h->h_dres[b];
+        memset(&r, 0, sizeof(r));
+        r.best_action = d.best_action;
+        r.best_win_flag = d.best_win_flag;
+        r.best_n = d.best_n;
+        r.best_n_wins = d.best_n_wins;
+        r.steps = h->last_steps;
+        r.playouts = d.playouts;
+        r.plies = d.plies;
+        r.ub_draws = d.ub_draws;
+        r.status = d.status;
+        r.n_root_actions = d.n_root_actions;
+        r.device_ms = h->last_ms;
+        r.max_depth = d.max_depth;
+        r.total_nodes = d.total_nodes;
+        r.depth_sum = d.depth_sum;
+        r.max_size = d.max_size;
+        for (int a = 0; a < A; a++) {
+            r.root_ns[a] = h->h_sums[(long long)b * 3 * A + a];
+            r.actions_ns[a] = h->h_sums[(long long)b * 3 * A + A + a];
+            r.actions_ns_wins[a] = h->h_sums[(long long)b * 3 * A + 2 * A + a];
+            r.actions_win_flags[a] = h->h_flags[(long long)b * 2 * A + a];
+            r.actions_expanded[a] = h->h_flags[(long long)b * 2 * A + A + a];
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+
+// ===================================================================================================================
+// C ABI
+
+extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
+    if (!cfg || !out) return MCTSNC_E_BAD_ARGUMENT;
+    *out = nullptr;
+    const mctsnc_config &c = *cfg;
+    if (c.variant < 0 || c.variant > 3 || c.n_trees < 1 || c.n_trees > 512 || c.n_playouts < 1 || c.n_playouts > 512 ||
+        (c.n_playouts & (c.n_playouts - 1)) != 0 || c.max_batch < 1 || c.node_capacity < 2 || c.max_tree_size < 1 ||
+        c.max_actions < 1 || c.max_actions > MCTSNC_MAX_ACTIONS || c.tree_offset < 0 ||
+        c.n_trees_global < c.tree_offset + c.n_trees || !(c.ucb_c >= 0.f))
+        return MCTSNC_E_BAD_ARGUMENT;
+    if (c.threads_per_tree != 0 && (c.threads_per_tree < 32 || c.threads_per_tree > 1024 || c.threads_per_tree % 32))
+        return MCTSNC_E_BAD_ARGUMENT;
+    if (c.game != MCTSNC_GAME_C4) return MCTSNC_E_UNSUPPORTED;
+    if (c.board_rows != c4::ROWS || c.board_cols != c4::COLS || c.max_actions != c4::A || c.extra_info_memory != c4::COLS)
+        return MCTSNC_E_UNSUPPORTED;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) {
+        cudaGetLastError();
+        return MCTSNC_E_NO_DEVICE;
+    }
+    if (c.device < 0 || c.device >= n_dev) return MCTSNC_E_BAD_ARGUMENT;
+    CUDA_TRY(cudaSetDevice(c.device));
+    mctsnc_handle *h = new (std::nothrow) mctsnc_handle();
+    if (!h) return MCTSNC_E_NO_MEMORY;
+    h->cfg = c;
+    if (h->cfg.node_capacity > h->cfg.max_tree_size) h->cfg.node_capacity = h->cfg.max_tree_size;
+    if (h->cfg.node_capacity < 2) h->cfg.node_capacity = 2;
+    h->A = c.max_actions;
+    // tpb table of the reference, src/mctsnc.py:360-370 (only the entries that influence results)
+    const int tpb_board = pow2ceil(c.board_rows * c.board_cols);
+    const int tpb_extra = pow2ceil(c.extra_info_memory < 1 ? 1 : c.extra_info_memory);
+    const int tpb_actions = pow2ceil(c.max_actions);
+    int tpb_r = tpb_board > tpb_extra ? tpb_board : tpb_extra;
+    if (tpb_r > 512) tpb_r = 512;
+    h->tpb_e1 = tpb_r > tpb_actions ? tpb_r : tpb_actions;
+    if (h->tpb_e1 > 512) h->tpb_e1 = 512;
+    h->tpb_roa = tpb_actions;
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, c.device));
+    h->sm_count = prop.multiProcessorCount;
+    h->n_trees_total = (long long)c.max_batch * c.n_trees;
+    const long long nodes = h->n_trees_total * h->cfg.node_capacity;
+    const bool ocp = is_ocp(c);
+    h->rng_per_search = ocp ? (long long)c.n_trees * c.n_playouts : (long long)c.n_trees * h->A * c.n_playouts;
+    h->dyn_smem = sizeof(ulonglong2) * (size_t)(h->rng_per_search / c.n_trees);
+    if (h->dyn_smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(search_kernel_ptr(c), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
+        if (e != cudaSuccess) {
+            delete h;
+            return (int)e;
+        }
+    }
+    int rc = 0;
+    if (!rc) rc = dev_alloc(h, &h->rec, nodes);
+    if (!rc) rc = dev_alloc(h, &h->board, nodes);
+    if (!rc) rc = dev_alloc(h, &h->parent, nodes);
+    if (!rc) rc = dev_alloc(h, &h->state, h->n_trees_total);
+    if (!rc) rc = dev_alloc(h, &h->paths, h->n_trees_total * PATH_CAP);
+    if (!rc) rc = dev_alloc(h, &h->actions_expanded, h->n_trees_total * (h->A + 2));
+    if (!rc) rc = dev_alloc(h, &h->child_out, h->n_trees_total * h->A * 2);
+    if (!rc) rc = dev_alloc(h, &h->rng_playout, h->rng_per_search * c.max_batch);
+    if (!rc) rc = dev_alloc(h, &h->rng_playout_base, h->rng_per_search);
+    if (!rc) rc = dev_alloc(h, &h->rng_expand, h->n_trees_total);
+    if (!rc) rc = dev_alloc(h, &h->rng_expand_base, (long long)c.n_trees);
+    if (!rc) rc = dev_alloc(h, &h->root_board, (long long)c.max_batch);
+    if (!rc) rc = dev_alloc(h, &h->root_turn, (long long)c.max_batch);
+    if (!rc) rc = dev_alloc(h, &h->sums, (long long)c.max_batch * 3 * h->A);
+    if (!rc) rc = dev_alloc(h, &h->flags, (long long)c.max_batch * 2 * h->A);
+    if (!rc) rc = dev_alloc(h, &h->dres, (long long)c.max_batch);
+    if (!rc && cudaMallocHost((void **)&h->h_root_board, sizeof(ulonglong2) * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaMallocHost((void **)&h->h_root_turn, c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaMallocHost((void **)&h->h_sums, sizeof(long long) * 3 * h->A * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaMallocHost((void **)&h->h_flags, (size_t)2 * h->A * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaMallocHost((void **)&h->h_dres, sizeof(DevResult) * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaEventCreate(&h->ev0) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaEventCreate(&h->ev1) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc) rc = (int)cudaMemset(h->state, 0, sizeof(TreeState) * h->n_trees_total);
+    if (!rc) rc = (int)cudaMemset(h->actions_expanded, 0, sizeof(short) * h->n_trees_total * (h->A + 2));
+    if (!rc) rc = (int)cudaMemset(h->child_out, 0, sizeof(int) * h->n_trees_total * h->A * 2);
+    if (rc) {
+        release(h);
+        delete h;
+        cudaGetLastError();
+        return rc;
+    }
+    *out = h;
+    rc = mctsnc_reset_rng(h);
+    if (rc) {
+        mctsnc_destroy(h);
+        *out = nullptr;
+    }
+    return rc;
+}
+
+extern "C" int mctsnc_destroy(mctsnc_handle *h) {
+    if (!h) return MCTSNC_E_BAD_ARGUMENT;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    release(h);
+    delete h;
+    return 0;
+}
+
+extern "C" int mctsnc_reset_rng(mctsnc_handle *h) {
+    if (!h) return MCTSNC_E_BAD_ARGUMENT;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    const mctsnc_config &c = h->cfg;
+    const bool ocp = is_ocp(c);
+    std::vector<ulonglong2> host((size_t)h->rng_per_search);
+    // playout streams: ACP stream (tree, action, t) = tree*A*P + action*P + t (src/mctsnc.py:1938, :2028),
+    // OCP stream (tree, t) = tree*P + t (cuda.grid(1), :1849); `tree` counts over the whole (sharded) search
+    const long long per_tree = ocp ? (long long)c.n_playouts : (long long)h->A * c.n_playouts;
+    make_streams(c.seed, (long long)c.tree_offset * per_tree, h->rng_per_search, 1, host.data());
+    CUDA_TRY(cudaMemcpy(h->rng_playout_base, host.data(), sizeof(ulonglong2) * host.size(), cudaMemcpyHostToDevice));
+    if (ocp) {
+        // the child pick of tree `tree` uses stream tree * tpb_e1 of a second array with the same seed (:391, :1385)
+        std::vector<ulonglong2> he((size_t)c.n_trees);
+        make_streams(c.seed, (long long)c.tree_offset * h->tpb_e1, c.n_trees, h->tpb_e1, he.data());
+        CUDA_TRY(cudaMemcpy(h->rng_expand_base, he.data(), sizeof(ulonglong2) * he.size(), cudaMemcpyHostToDevice));
+    }
+    int rc = seed_streams(h, c.max_batch, 0);
+    if (rc) return rc;
+    CUDA_TRY(cudaDeviceSynchronize());
+    return 0;
+}
+
+extern "C" int mctsnc_run(mctsnc_handle *h, const int8_t *board, const int8_t *extra_info, int32_t turn, int64_t steps_limit,
+                          double time_limit_s, mctsnc_result *out) {
+    if (!h || !board || !out) return MCTSNC_E_BAD_ARGUMENT;
+    if (steps_limit < 0 && !(time_limit_s > 0)) return MCTSNC_E_BAD_ARGUMENT;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    const int8_t t8 = (int8_t)turn;
+    h->staged_roots = 0;
+    int rc = stage_roots(h, 1, board, extra_info, &t8, 0);
+    if (rc) return rc;
+    h->staged_roots = 1;
+    const auto t0 = std::chrono::steady_clock::now();
+    long long done = 0;
+    float total_ms = 0.f;
+    int chunk = steps_limit >= 0 && !(time_limit_s > 0) ? (int)(steps_limit > 1000000 ? 1000000 : steps_limit) : 16;
+    int first = 1;
+    for (;;) {
+        bool stop = steps_limit >= 0 && done >= steps_limit;
+        if (!stop && time_limit_s > 0) {
+            const double el = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            stop = el >= time_limit_s;
+        }
+        if (stop && !first) break;
+        long long n = stop ? 0 : chunk;  // a search without a single step still resets the trees to the root
+        if (steps_limit >= 0 && done + n > steps_limit) n = steps_limit - done;
+        CUDA_TRY(cudaEventRecord(h->ev0, 0));
+        rc = launch_search(h, 1, (int)n, first, 0);
+        if (rc) return rc;
+        CUDA_TRY(cudaEventRecord(h->ev1, 0));
+        CUDA_TRY(cudaEventSynchronize(h->ev1));
+        float ms = 0.f;
+        CUDA_TRY(cudaEventElapsedTime(&ms, h->ev0, h->ev1));
+        total_ms += ms;
+        done += n;
+        first = 0;
+        if (stop) break;
+        if (time_limit_s > 0 && n > 0) {
+            // aim at launches of about 2 ms so that the clock is read often enough
+            const double per_step = ms / (double)n;
+            int next = per_step > 0 ? (int)(2.0 / per_step) : chunk * 2;
+            if (next < 1) next = 1;
+            if (next > 4096) next = 4096;
+            chunk = next;
+        }
+    }
+    h->last_ms = total_ms;
+    h->last_steps = done;
+    rc = launch_reduce_trees(h, 1, h->sums, 0);
+    if (rc) return rc;
+    rc = launch_reduce_actions(h, 1, h->sums, 0);
+    if (rc) return rc;
+    return fetch_results(h, 1, h->sums, out, 0);
+}
+
+extern "C" int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards, const int8_t *extras,
+                                          const int8_t *turns, int64_t steps, int32_t reseed, int64_t *partial_sums_device,
+                                          void *stream) {
+    if (!h || (boards && !turns) || batch < 1 || steps < 0 || steps > 0x7fffffff) return MCTSNC_E_BAD_ARGUMENT;
+    if (batch > h->cfg.max_batch) return MCTSNC_E_CAPACITY;
+    if (!boards && batch > h->staged_roots) return MCTSNC_E_BAD_ARGUMENT;  // nothing staged to search again
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc = 0;
+    if (boards) {
+        h->staged_roots = 0;
+        rc = stage_roots(h, batch, boards, extras, turns, s);
+        if (rc) return rc;
+        h->staged_roots = batch;
+    }
+    if (reseed) {
+        rc = seed_streams(h, batch, s);
+        if (rc) return rc;
+    }
+    CUDA_TRY(cudaEventRecord(h->ev0, s));
+    rc = launch_search(h, batch, (int)steps, 1, s);
+    if (rc) return rc;
+    CUDA_TRY(cudaEventRecord(h->ev1, s));
+    h->last_steps = steps;
+    return launch_reduce_trees(h, batch, partial_sums_device ? (long long *)partial_sums_device : h->sums, s);
+}
+
+extern "C" int mctsnc_finish_batch_device(mctsnc_handle *h, int32_t batch, const int64_t *summed_device, mctsnc_result *results,
+                                          void *stream) {
+    if (!h || batch < 1) return MCTSNC_E_BAD_ARGUMENT;
+    if (batch > h->cfg.max_batch) return MCTSNC_E_CAPACITY;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long *sums = summed_device ? (const long long *)summed_device : h->sums;
+    int rc = launch_reduce_actions(h, batch, sums, s);
+    if (rc) return rc;
+    if (!results) return 0;  // the caller keeps everything on the device
+    CUDA_TRY(cudaEventSynchronize(h->ev1));
+    CUDA_TRY(cudaEventElapsedTime(&h->last_ms, h->ev0, h->ev1));
+    return fetch_results(h, batch, sums, results, s);
+}
+
+extern "C" int mctsnc_run_batch(mctsnc_handle *h, int32_t batch, const int8_t *boards, const int8_t *extras, const int8_t *turns,
+                                int64_t steps, int32_t reseed, mctsnc_result *results) {
+    int rc = mctsnc_search_batch_device(h, batch, boards, extras, turns, steps, reseed, nullptr, nullptr);
+    if (rc) return rc;
+    return mctsnc_finish_batch_device(h, batch, nullptr, results, nullptr);
+}
+
+extern "C" int mctsnc_export(mctsnc_handle *h, int32_t search, int32_t field, void *dst, int64_t max_nodes) {
+    if (!h || !dst || search < 0 || search >= h->cfg.max_batch) return MCTSNC_E_BAD_ARGUMENT;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    const int T = h->cfg.n_trees, A = h->A;
+    const long long cap = h->cfg.node_capacity;
+    const long long g0 = (long long)search * T;
+    std::vector<TreeState> st(T);
+    CUDA_TRY(cudaMemcpy(st.data(), h->state + g0, sizeof(TreeState) * T, cudaMemcpyDeviceToHost));
+    switch (field) {
+    case MCTSNC_F_SIZES:
+        for (int t = 0; t < T; t++) ((int32_t *)dst)[t] = st[t].size;
+        return 0;
+    case MCTSNC_F_NODES_SELECTED:
+        for (int t = 0; t < T; t++) ((int32_t *)dst)[t] = st[t].selected;
+        return 0;
+    case MCTSNC_F_PLAYOUT_OUTCOMES:
+        for (int t = 0; t < T; t++) {
+            ((int32_t *)dst)[2 * t] = st[t].out_neg;
+            ((int32_t *)dst)[2 * t + 1] = st[t].out_pos;
+        }
+        return 0;
+    case MCTSNC_F_SELECTED_PATHS: {
+        std::vector<int> paths((size_t)T * PATH_CAP);
+        CUDA_TRY(cudaMemcpy(paths.data(), h->paths + g0 * PATH_CAP, sizeof(int) * paths.size(), cudaMemcpyDeviceToHost));
+        int32_t *o = (int32_t *)dst;
+        memset(o, 0, sizeof(int32_t) * T * (MAX_TREE_DEPTH + 2));
+        for (int t = 0; t < T; t++) {
+            for (int e = 0; e < st[t].path_len && e < PATH_CAP; e++) o[(long long)t * (MAX_TREE_DEPTH + 2) + e] = paths[(size_t)t * PATH_CAP + e];
+            o[(long long)t * (MAX_TREE_DEPTH + 2) + MAX_TREE_DEPTH + 1] = st[t].path_len;
+        }
+        return 0;
+    }
+    case MCTSNC_F_ACTIONS_EXPANDED:
+        CUDA_TRY(cudaMemcpy(dst, h->actions_expanded + g0 * (A + 2), sizeof(short) * T * (A + 2), cudaMemcpyDeviceToHost));
+        return 0;
+    case MCTSNC_F_PLAYOUT_OUTCOMES_CHILDREN:
+        CUDA_TRY(cudaMemcpy(dst, h->child_out + g0 * A * 2, sizeof(int) * T * A * 2, cudaMemcpyDeviceToHost));
+        return 0;
+    default:
+        break;
+    }
+    if (field < 0 || field > MCTSNC_F_EXTRA_INFOS || max_nodes < 1) return MCTSNC_E_BAD_ARGUMENT;
+    const int cells = h->cfg.board_rows * h->cfg.board_cols;
+    const int extra = h->cfg.extra_info_memory;
+    std::vector<int4> rec;
+    std::vector<ulonglong2> brd;
+    std::vector<int> par;
+    for (int t = 0; t < T; t++) {
+        long long n = st[t].size < max_nodes ? st[t].size : max_nodes;
+        if (n > cap) n = cap;
+        rec.resize((size_t)n);
+        CUDA_TRY(cudaMemcpy(rec.data(), h->rec + (g0 + t) * cap, sizeof(int4) * n, cudaMemcpyDeviceToHost));
+        if (field == MCTSNC_F_TREES) {
+            par.resize((size_t)n);
+            CUDA_TRY(cudaMemcpy(par.data(), h->parent + (g0 + t) * cap, sizeof(int) * n, cudaMemcpyDeviceToHost));
+        }
+        if (field == MCTSNC_F_BOARDS || field == MCTSNC_F_EXTRA_INFOS) {
+            brd.resize((size_t)n);
+            CUDA_TRY(cudaMemcpy(brd.data(), h->board + (g0 + t) * cap, sizeof(ulonglong2) * n, cudaMemcpyDeviceToHost));
+        }
+        for (long long i = 0; i < max_nodes; i++) {
+            const bool valid = i < n;
+            const int4 r = valid ? rec[(size_t)i] : make_int4(0, 0, -1, 0);
+            const long long o = (long long)t * max_nodes + i;
+            switch (field) {
+            case MCTSNC_F_TREES: {
+                int32_t *row = (int32_t *)dst + o * (1 + A);
+                row[0] = valid ? par[(size_t)i] : -1;
+                const unsigned mask = r.w & 0x7F;
+                int k = 0;
+                for (int a = 0; a < A; a++) row[1 + a] = (valid && ((mask >> a) & 1u)) ? r.z + k++ : -1;
+                break;
+            }
+            case MCTSNC_F_DEPTHS: ((int16_t *)dst)[o] = valid ? (int16_t)meta_depth(r.w) : 0; break;
+            case MCTSNC_F_TURNS: ((int8_t *)dst)[o] = valid ? (int8_t)meta_turn(r.w) : 0; break;
+            case MCTSNC_F_LEAVES: ((uint8_t *)dst)[o] = valid ? ((r.w & 0x7F) == 0) : 0; break;
+            case MCTSNC_F_TERMINALS: ((uint8_t *)dst)[o] = valid ? ((r.w & META_TERMINAL) != 0) : 0; break;
+            case MCTSNC_F_OUTCOMES: ((int8_t *)dst)[o] = valid ? (int8_t)meta_outcome(r.w) : 0; break;
+            case MCTSNC_F_NS: ((int32_t *)dst)[o] = valid ? r.x : 0; break;
+            case MCTSNC_F_NS_WINS: ((int32_t *)dst)[o] = valid ? r.y : 0; break;
+            case MCTSNC_F_BOARDS: {
+                int8_t *bo = (int8_t *)dst + o * cells;
+                memset(bo, 0, cells);
+                if (valid)
+                    for (int j = 0; j < c4::COLS; j++)
+                        for (int hgt = 0; hgt < c4::ROWS; hgt++) {
+                            const int bit = 7 * j + hgt;
+                            const int v = ((brd[(size_t)i].y >> bit) & 1ULL) ? 1 : (((brd[(size_t)i].x >> bit) & 1ULL) ? -1 : 0);
+                            bo[(c4::ROWS - 1 - hgt) * c4::COLS + j] = (int8_t)v;
+                        }
+                break;
+            }
+            case MCTSNC_F_EXTRA_INFOS: {
+                int8_t *eo = (int8_t *)dst + o * extra;
+                memset(eo, 0, extra);
+                if (valid) {
+                    const unsigned long long all = brd[(size_t)i].x | brd[(size_t)i].y;
+                    for (int j = 0; j < c4::COLS; j++) eo[j] = (int8_t)__builtin_popcountll((all >> (7 * j)) & 0x3FULL);
+                }
+                break;
+            }
+            }
+        }
+    }
+    return 0;
+}
+
+extern "C" int mctsnc_export_rng(mctsnc_handle *h, int32_t search, int32_t which, uint64_t *dst, int64_t n) {
+    if (!h || !dst || search < 0 || search >= h->cfg.max_batch || n < 0) return MCTSNC_E_BAD_ARGUMENT;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    if (which == 0) {
+        if (n > h->rng_per_search) return MCTSNC_E_BAD_ARGUMENT;
+        CUDA_TRY(cudaMemcpy(dst, h->rng_playout + (long long)search * h->rng_per_search, sizeof(ulonglong2) * n, cudaMemcpyDeviceToHost));
+    } else {
+        if (!is_ocp(h->cfg) || n > h->cfg.n_trees) return MCTSNC_E_BAD_ARGUMENT;
+        CUDA_TRY(cudaMemcpy(dst, h->rng_expand + (long long)search * h->cfg.n_trees, sizeof(ulonglong2) * n, cudaMemcpyDeviceToHost));
+    }
+    return 0;
+}
+
+extern "C" int mctsnc_query(mctsnc_handle *h, int32_t *threads_per_tree, int32_t *blocks_per_sm, int32_t *sm_count,
+                            int64_t *bytes_allocated) {
+    if (!h) return MCTSNC_E_BAD_ARGUMENT;
+    if (threads_per_tree) *threads_per_tree = h->threads;
+    if (blocks_per_sm) *blocks_per_sm = h->blocks_per_sm;
+    if (sm_count) *sm_count = h->sm_count;
+    if (bytes_allocated) *bytes_allocated = h->bytes;
+    return 0;
+}
+
+extern "C" const char *mctsnc_error_string(int code) {
+    switch (code) {
+    case 0: return "success";
+    case MCTSNC_E_BAD_ARGUMENT: return "mctsnc: bad argument";
+    case MCTSNC_E_UNSUPPORTED: return "mctsnc: game or shape not supported by this build";
+    case MCTSNC_E_NO_MEMORY: return "mctsnc: out of memory";
+    case MCTSNC_E_BAD_ROOT: return "mctsnc: root board and extra_info do not describe a reachable, unfinished position";
+    case MCTSNC_E_CAPACITY: return "mctsnc: batch or step count beyond the capacity of the handle";
+    case MCTSNC_E_NO_DEVICE: return "mctsnc: no CUDA device";
+    default: break;
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "mctsnc: unknown error";
+}
