@@ -10,7 +10,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmctsnc_b200.so")
+LIB_PATH = os.environ.get("MCTSNC_B200_LIB") or os.path.join(HERE, "libmctsnc_b200.so")
 
 MAX_ACTIONS = 512
 GAME_C4, GAME_GOMOKU = 0, 1

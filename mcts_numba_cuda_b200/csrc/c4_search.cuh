@@ -24,16 +24,19 @@ constexpr unsigned long long BOTTOM_ROW = 0x0000040810204081ULL;  // bit 7c for 
 constexpr unsigned long long TOP_ROW = BOTTOM_ROW << 5;
 constexpr unsigned long long FULL_BOARD = BOTTOM_ROW * 0x3FULL;
 
+// four in a row anywhere in the stone set p.  Left shifts: the low word of a 64-bit left shift is a plain 32-bit
+// shift, which the integer multiply-add pipe can execute, taking load off the logic pipe that limits this kernel.
+// Bits shifted past bit 48 meet zeros of p in the AND.
 __host__ __device__ __forceinline__ bool has_four(unsigned long long p) {
     unsigned long long m, r;
-    m = p & (p >> 7);
-    r = m & (m >> 14);
-    m = p & (p >> 6);
-    r |= m & (m >> 12);
-    m = p & (p >> 8);
-    r |= m & (m >> 16);
-    m = p & (p >> 1);
-    r |= m & (m >> 2);
+    m = p & (p << 7);
+    r = m & (m << 14);
+    m = p & (p << 6);
+    r |= m & (m << 12);
+    m = p & (p << 8);
+    r |= m & (m << 16);
+    m = p & (p << 1);
+    r |= m & (m << 2);
     return r != 0;
 }
 
@@ -72,6 +75,8 @@ struct EmuResult {
     int outcome;
     unsigned plies;
     unsigned ub;
+    unsigned err;
+    unsigned long long s0, s1;  // stream state after the game
 };
 
 __device__ __forceinline__ int emu_cell(const signed char *board, int i, int j, unsigned &err) {
@@ -96,7 +101,8 @@ __device__ __forceinline__ int emu_line(const signed char *board, int i, int j, 
 }
 
 __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsigned long long pos, int turn,
-                                                   unsigned long long &s0, unsigned long long &s1, unsigned &err) {
+                                                   unsigned long long s0, unsigned long long s1) {
+    unsigned err = 0;
     signed char board[ROWS * COLS];
     signed char fills[COLS];
     short legal[COLS + 1];
@@ -111,7 +117,7 @@ __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsig
         fills[j] = (signed char)f;
     }
     for (int j = 0; j <= COLS; j++) legal[j] = 0;
-    EmuResult r = {2, 0u, 0u};
+    EmuResult r = {2, 0u, 0u, 0u, 0ULL, 0ULL};
     for (;;) {
         int count = 0;
         for (int j = 0; j < COLS; j++)
@@ -148,13 +154,15 @@ __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsig
                 if (fills[j] < ROWS) draw = false;
             if (draw) out = 0;
         }
-        if (out != 2) {
-            r.outcome = out;
-            return r;
-        }
         if (r.plies > 4096u) {  // cannot happen; keeps the loop bounded whatever the memory holds
             err = 1;
-            r.outcome = 0;
+            out = 0;
+        }
+        if (out != 2) {
+            r.outcome = out;
+            r.err = err;
+            r.s0 = s0;
+            r.s1 = s1;
             return r;
         }
     }
@@ -162,21 +170,32 @@ __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsig
 
 // ---------------------------------------------------------------------------------------------------------------
 
+// everything a thread needs to start a game from one child, fetched with two 16-byte shared-memory loads
+struct __align__(16) GameSlot {
+    unsigned long long cur;  // stones of the side to move
+    unsigned long long all;  // all stones
+    unsigned legal;          // columns with room
+    int rng_base;            // index of the child's first stream in the block's stream array
+    int stones;              // stones on the board
+    float count;             // number of columns with room
+};
+
 struct Shared {
+    GameSlot slot[A];        // children that need real playouts, in expansion order
+    int tally[A][2];         // per slot: games won by -1, by +1
     int path[48];
     int path_ns[48];
     int path_wins[48];
-    unsigned long long child_neg[A];
-    unsigned long long child_pos[A];
-    int child_action[A];
-    int child_outcome[A];   // 2 = ongoing
-    unsigned child_legal[A]; // columns with room in the child's position
-    int tally[A][2];        // per expanded child: games won by -1, by +1
-    int active[A];          // children that need real playouts
-    int child_out[A][2];    // trees_playout_outcomes_children (persists over steps)
-    short ae[A + 2];        // trees_actions_expanded row (persists over steps)
-    unsigned lut[128];      // lut[set] packs, 3 bits each, the columns of `set` in ascending order
-    int n_active;
+    int child_action[A];     // per expanded child (expansion order): its action,
+    int child_outcome[A];    // its outcome (2 = ongoing)
+    int child_slot[A];       // and its slot (-1: no playouts: terminal, or not picked in OCP)
+    int child_out[A][2];     // trees_playout_outcomes_children (persists over steps)
+    short ae[A + 2];         // trees_actions_expanded row (persists over steps)
+    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the bit position of the
+    // column's bottom cell (7 * column) in the low byte and the column's bit (1 << column) in the high byte
+    unsigned short move_lut[128 * 8];
+    int n_slots;
+    int next_item;           // next game to hand out in the playout phase
     int n_exp;
     int mode;
     int first_child;
@@ -184,7 +203,7 @@ struct Shared {
     int selected;
     int sel_meta;
     int path_len;
-    int pick;               // OCP: index (among expanded children) of the child that is played out
+    int pick;                // OCP: index (among expanded children) of the child that is played out
     int root_turn;
     int size;
     int out_neg, out_pos;
@@ -214,12 +233,15 @@ __global__ void search_kernel(const SearchParams p) {
     const int n_streams = OCP ? P : A * P;
     ulonglong2 *g_rng = p.rng_playout + (long long)g * n_streams;
     for (int i = tid; i < n_streams; i += nt) s_rng[i] = g_rng[i];
-    for (int i = tid; i < 128; i += nt) {
-        unsigned packed = 0;
-        int k = 0;
+    for (int i = tid; i < 128 * 8; i += nt) {
+        const int set = i >> 3, ord = i & 7;
+        int col = 0, seen = 0;
         for (int c = 0; c < COLS; c++)
-            if (i & (1 << c)) packed |= (unsigned)c << (3 * k++);
-        s.lut[i] = packed;
+            if (set & (1 << c)) {
+                if (seen == ord) col = c;
+                seen++;
+            }
+        s.move_lut[i] = (unsigned short)((7 * col) | ((1 << col) << 8));
     }
     if (tid == 0) {
         const int b = g / p.n_trees;
@@ -307,15 +329,13 @@ __global__ void search_kernel(const SearchParams p) {
             }
             // ------------------------------------------------------- expand (_expand_1_* and _expand_2_*)
             const int sel_turn = meta_turn(r.w);
-            const int sel_depth = meta_depth(r.w);
-            int mode, n_exp = 0, exp_mask = 0, first_child = -1;
+            int mode, n_exp = 0, exp_mask = 0, first_child = -1, pick = 0, n_slots = 0;
             if (r.w & META_TERMINAL) {
                 mode = MODE_TERMINAL;
                 if (lane == 0) {
                     const int o = meta_outcome(r.w);
                     s.out_neg = o == -1 ? P : 0;
                     s.out_pos = o == 1 ? P : 0;
-                    s.n_active = 0;
                 }
             } else {
                 const ulonglong2 bb = board[node];  // x: stones of -1, y: stones of +1
@@ -332,31 +352,9 @@ __global__ void search_kernel(const SearchParams p) {
                 if (n_exp > 0) {
                     mode = MODE_ALL_CHILDREN;
                     first_child = s.size;
-                    if (lane < A && ((exp_mask >> lane) & 1)) {
-                        const int k = __popc(exp_mask & ((1 << lane) - 1));
-                        const unsigned long long move = (all + (1ULL << (7 * lane))) & (0x3FULL << (7 * lane));
-                        unsigned long long cneg = bb.x, cpos = bb.y;
-                        if (sel_turn > 0) cpos |= move;
-                        else cneg |= move;
-                        const bool win = has_four(sel_turn > 0 ? cpos : cneg);
-                        const bool full = (all | move) == FULL_BOARD;
-                        const int outcome = win ? sel_turn : (full ? 0 : 2);
-                        board[first_child + k] = make_ulonglong2(cneg, cpos);
-                        parent[first_child + k] = node;
-                        s.child_neg[k] = cneg;
-                        s.child_pos[k] = cpos;
-                        s.child_action[k] = lane;
-                        s.child_outcome[k] = outcome;
-                        s.child_legal[k] = legal_columns(all | move);
-                        s.tally[k][0] = outcome == -1 ? P : 0;
-                        s.tally[k][1] = outcome == 1 ? P : 0;
-                    }
-                    __syncwarp();
-                    if (lane == 0) {
-                        s.size += n_exp;
-                        int pick = 0;
-                        if (OCP) {
-                            // src/mctsnc.py:1435 / :1511 -- float32 * int64 is a float64 product, truncated
+                    if (OCP) {
+                        // src/mctsnc.py:1435 / :1511 -- float32 * int64 is a float64 product, truncated
+                        if (lane == 0) {
                             ulonglong2 es = p.rng_expand[g];
                             const float u = rng_uniform_f32(es.x, es.y);
                             p.rng_expand[g] = es;
@@ -366,33 +364,59 @@ __global__ void search_kernel(const SearchParams p) {
                                 s.ub++;
                                 s.status |= STATUS_UB_DRAW;
                             }
-                            s.pick = pick;
                         }
-                        int na = 0;
-                        for (int k = 0; k < n_exp; k++) {
-                            if (OCP && k != pick) {
-                                s.tally[k][0] = 0;
-                                s.tally[k][1] = 0;
-                                continue;
-                            }
-                            if (s.child_outcome[k] == 2) s.active[na++] = k;
+                        pick = __shfl_sync(0xFFFFFFFFu, pick, 0);
+                    }
+                    const bool has_child = lane < A && ((exp_mask >> lane) & 1);
+                    const int k = __popc(exp_mask & ((1 << lane) - 1));
+                    unsigned long long cneg = bb.x, cpos = bb.y, call = all;
+                    int outcome = 2;
+                    if (has_child) {
+                        const unsigned long long move = (all + (1ULL << (7 * lane))) & (0x3FULL << (7 * lane));
+                        if (sel_turn > 0) cpos |= move;
+                        else cneg |= move;
+                        call = all | move;
+                        const bool win = has_four(sel_turn > 0 ? cpos : cneg);
+                        outcome = win ? sel_turn : (call == FULL_BOARD ? 0 : 2);
+                        board[first_child + k] = make_ulonglong2(cneg, cpos);
+                        parent[first_child + k] = node;
+                    }
+                    const bool plays = has_child && outcome == 2 && (!OCP || k == pick);
+                    const unsigned play_mask = __ballot_sync(0xFFFFFFFFu, plays);
+                    n_slots = __popc(play_mask);
+                    if (has_child) {
+                        const int j = plays ? __popc(play_mask & ((1u << lane) - 1u)) : -1;
+                        s.child_action[k] = lane;
+                        s.child_outcome[k] = outcome;
+                        s.child_slot[k] = j;
+                        if (plays) {
+                            GameSlot gs;
+                            gs.cur = sel_turn > 0 ? cneg : cpos;  // the child is to be moved in by the other side
+                            gs.all = call;
+                            gs.legal = legal_columns(call);
+                            gs.rng_base = OCP ? 0 : lane * P;
+                            gs.stones = __popcll(call);
+                            gs.count = (float)__popc(gs.legal);
+                            s.slot[j] = gs;
+                            s.tally[j][0] = 0;
+                            s.tally[j][1] = 0;
                         }
-                        s.n_active = na;
                     }
                 } else {
                     // no room for a single child: the selected node itself is played out
                     mode = MODE_TREE_FULL;
+                    n_slots = 1;
                     if (lane == 0) {
-                        s.child_neg[0] = bb.x;
-                        s.child_pos[0] = bb.y;
-                        s.child_action[0] = 0;
-                        s.child_outcome[0] = 2;
-                        s.child_legal[0] = legal;
+                        GameSlot gs;
+                        gs.cur = sel_turn > 0 ? bb.y : bb.x;
+                        gs.all = all;
+                        gs.legal = legal;
+                        gs.rng_base = 0;
+                        gs.stones = __popcll(all);
+                        gs.count = (float)n_legal;
+                        s.slot[0] = gs;
                         s.tally[0][0] = 0;
                         s.tally[0][1] = 0;
-                        s.active[0] = 0;
-                        s.n_active = 1;
-                        s.pick = 0;
                     }
                 }
             }
@@ -409,11 +433,15 @@ __global__ void search_kernel(const SearchParams p) {
             }
             __syncwarp();
             if (lane == 0) {
+                if (mode == MODE_ALL_CHILDREN) s.size += n_exp;
                 s.ae[A + 1] = (short)(mode == MODE_ALL_CHILDREN ? n_exp : 1);
                 int m2 = mode;
-                if (OCP && mode == MODE_ALL_CHILDREN) m2 = thrifty ? s.pick : s.child_action[s.pick];
+                if (OCP && mode == MODE_ALL_CHILDREN) m2 = thrifty ? pick : s.child_action[pick];
                 s.ae[A] = (short)m2;
                 if (!OCP && mode != MODE_ALL_CHILDREN) s.ae[0] = 0;
+                s.next_item = 0;
+                s.n_slots = n_slots;
+                s.pick = pick;
                 s.mode = mode;
                 s.n_exp = n_exp;
                 s.exp_mask = exp_mask;
@@ -422,79 +450,96 @@ __global__ void search_kernel(const SearchParams p) {
                 s.sel_meta = r.w;
                 s.path_len = depth + 1;
             }
-            (void)sel_depth;
         }
         __syncthreads();
 
         // =========================================================== playouts (all threads)
+        // Games are handed out one at a time from a counter in shared memory, so the threads of the block stay busy
+        // until the step's games run out whatever their lengths.  Game `item` is playout t = item % P of slot
+        // item / P; it draws from the stream the reference's thread (tree, action, t) owns (src/mctsnc.py:1938, :2028;
+        // OCP: cuda.grid(1), :1849), so which thread plays it does not matter.
         {
-            const int n_items = s.n_active << p.log2_playouts;
-            const int child_turn = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
-            int item = tid;
-            bool running = item < n_items;
-            // state of the game in flight
+            const int n_items = s.n_slots << p.log2_playouts;
+            // the side to move in the played-out positions: the other side than at the selected node, unless the
+            // selected node itself is played out
+            const int first_mover = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
             unsigned long long cur = 0, all = 0, s0 = 0, s1 = 0;
             unsigned legal = 0;
-            int cnt = 0, turn = 0, k = 0;
-            unsigned plies_at_start = 0;
-            int rng_idx = 0;
-            bool fresh = true;
-            while (running) {
-                if (fresh) {
-                    k = s.active[item >> p.log2_playouts];
-                    const int t = item & (P - 1);
-                    // src/mctsnc.py:1938 / :2028 (ACP: stream (tree, action, t)), cuda.grid(1) at :1849 (OCP: (tree, t))
-                    rng_idx = OCP ? t : s.child_action[k] * P + t;
-                    const ulonglong2 rs = s_rng[rng_idx];
-                    s0 = rs.x;
-                    s1 = rs.y;
-                    const unsigned long long cneg = s.child_neg[k], cpos = s.child_pos[k];
-                    turn = child_turn;
-                    all = cneg | cpos;
-                    cur = turn > 0 ? cpos : cneg;
-                    legal = s.child_legal[k];
-                    cnt = __popc(legal);
-                    plies_at_start = my_plies;
-                    fresh = false;
-                }
+            float count = 0.f;
+            int rng_idx = 0, stones = 0, j = 0;
+            int item = atomicAdd(&s.next_item, 1);
+            if (item < n_items) {
+                j = item >> p.log2_playouts;
+                const GameSlot gs = s.slot[j];
+                cur = gs.cur;
+                all = gs.all;
+                legal = gs.legal;
+                count = gs.count;
+                stones = gs.stones;
+                rng_idx = gs.rng_base + (item & (P - 1));
+                const ulonglong2 rs = s_rng[rng_idx];
+                s0 = rs.x;
+                s1 = rs.y;
+            }
+            while (item < n_items) {
                 // ---- one ply (src/mctsnc.py:2059-2064, :2069)
                 const float u = rng_uniform_f32(s0, s1);
-                const int ord = __float2int_rz(__fmul_rn(u, (float)cnt));
-                int outcome = 2;
-                if (ord >= cnt) {
+                const float prod = __fmul_rn(u, count);  // float32 * int16 -> float32 (:2061)
+                bool win, over;
+                int emu_outcome = 2;
+                if (prod >= count) {
                     // u == 1.0f: replay this game through the byte-level emulation of the reference
+                    const GameSlot gs = s.slot[j];
                     const ulonglong2 rs = s_rng[rng_idx];
-                    s0 = rs.x;
-                    s1 = rs.y;
-                    const EmuResult er = playout_emulated(s.child_neg[k], s.child_pos[k], child_turn, s0, s1, my_err);
-                    outcome = er.outcome;
-                    my_plies = plies_at_start + er.plies;  // the abandoned attempt is not counted twice
+                    const unsigned long long other = gs.all ^ gs.cur;
+                    const EmuResult er = playout_emulated(first_mover > 0 ? other : gs.cur, first_mover > 0 ? gs.cur : other,
+                                                          first_mover, rs.x, rs.y);
+                    s0 = er.s0;
+                    s1 = er.s1;
+                    emu_outcome = er.outcome;
+                    my_plies += er.plies;
                     my_ub += er.ub;
+                    my_err |= er.err;
+                    all = 0;  // the plies of the replay are counted above, none from the bitboards
+                    stones = 0;
+                    win = false;
+                    over = true;
                 } else {
-                    const int col = (s.lut[legal] >> (3 * ord)) & 7;
-                    const unsigned long long nall = all | (all + (1ULL << (7 * col)));
-                    const unsigned long long mine = cur | (nall ^ all);
+                    const int ord = __float2int_rz(prod);
+                    const unsigned e = s.move_lut[legal * 8 + ord];
+                    const unsigned long long nall = all | (all + (1ULL << (e & 0xFF)));
+                    const unsigned long long move = nall ^ all;
+                    const unsigned long long mine = cur | move;
                     cur = all ^ cur;
                     all = nall;
-                    my_plies++;
-                    if (has_four(mine)) {
-                        outcome = turn;
-                    } else {
-                        if ((all >> (7 * col + 5)) & 1ULL) {
-                            legal &= ~(1u << col);
-                            cnt--;
-                        }
-                        if (cnt == 0) outcome = 0;
+                    win = has_four(mine);
+                    if ((move & TOP_ROW) != 0) {
+                        legal ^= e >> 8;
+                        count -= 1.0f;
                     }
-                    turn = -turn;
+                    over = win || count == 0.0f;
                 }
-                if (outcome != 2) {
+                if (over) {
                     s_rng[rng_idx] = make_ulonglong2(s0, s1);
-                    if (outcome < 0) atomicAdd(&s.tally[k][0], 1);
-                    else if (outcome > 0) atomicAdd(&s.tally[k][1], 1);
-                    item += nt;
-                    running = item < n_items;
-                    fresh = true;
+                    const int n = __popcll(all) - stones;  // plies of this game; the last one was made by the first
+                    my_plies += n;                         // mover iff n is odd
+                    int winner = emu_outcome == 2 ? 0 : emu_outcome;
+                    if (win) winner = (n & 1) ? first_mover : -first_mover;
+                    if (winner != 0) atomicAdd(&s.tally[j][winner > 0 ? 1 : 0], 1);
+                    item = atomicAdd(&s.next_item, 1);
+                    if (item < n_items) {
+                        j = item >> p.log2_playouts;
+                        const GameSlot gs = s.slot[j];
+                        cur = gs.cur;
+                        all = gs.all;
+                        legal = gs.legal;
+                        count = gs.count;
+                        stones = gs.stones;
+                        rng_idx = gs.rng_base + (item & (P - 1));
+                        const ulonglong2 rs = s_rng[rng_idx];
+                        s0 = rs.x;
+                        s1 = rs.y;
+                    }
                 }
             }
         }
@@ -511,10 +556,17 @@ __global__ void search_kernel(const SearchParams p) {
             if (mode == MODE_ALL_CHILDREN) {
                 int my_neg = 0, my_pos = 0;
                 if (lane < n_exp) {
-                    my_neg = s.tally[lane][0];
-                    my_pos = s.tally[lane][1];
-                    const bool played = !OCP || lane == s.pick;
                     const int o = s.child_outcome[lane];
+                    const int j = s.child_slot[lane];
+                    const bool played = !OCP || lane == s.pick;
+                    if (j >= 0) {
+                        my_neg = s.tally[j][0];
+                        my_pos = s.tally[j][1];
+                    } else if (played) {
+                        // a terminal child: its stored outcome stands for all P playouts (src/mctsnc.py:2016-2021)
+                        my_neg = o == -1 ? P : 0;
+                        my_pos = o == 1 ? P : 0;
+                    }
                     // children start from ns = ns_wins = 0 (src/mctsnc.py:1819-1820), then _backup_1_acp_* / the
                     // thread-0 part of _backup_ocp credit them (:2172-2177, :2104-2114)
                     const int cns = played ? P : 0;
@@ -552,6 +604,7 @@ __global__ void search_kernel(const SearchParams p) {
                     *reinterpret_cast<int2 *>(&rec[node]) = make_int2(ns, wins);
                 }
             }
+            __syncwarp();
             if (lane == 0) {
                 s.out_neg = neg_tot;
                 s.out_pos = pos_tot;
