@@ -1,0 +1,179 @@
+"""More GPU parity cases: the random streams, time-limited (multi-launch) searches, sharded handles, and the
+full-size headline workload checked through size-independent invariants."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from mcts_numba_cuda_b200 import MCTSNC, _abi
+from mcts_numba_cuda_b200.roots import c4_random_roots
+from oracle import oracle as om
+from oracle.oracle import OracleMCTSNC
+from tests.test_gpu_parity_c4 import compare_trees
+
+pytestmark = pytest.mark.gpu
+
+
+def _streams(ai, which, n, search=0):
+    out = np.zeros((n, 2), dtype=np.uint64)
+    _abi.check(_abi.lib().mctsnc_export_rng(ai._handle, search, which, out.ctypes.data, n))
+    return out
+
+
+def test_streams_equal_numba_layout():
+    """ACP: stream (tree, action, t) = state[tree*A*P + action*P + t] of create_xoroshiro128p_states(T*A*P, seed)
+    (src/mctsnc.py:394, :2028); OCP: playout stream (tree, t) = state[tree*P + t], child-pick stream of tree =
+    state[tree*tpb_e1] of a second array with the same seed (:391-392, :1385)."""
+    ai = MCTSNC((6, 7), 7, 7, search_steps_limit=5, search_time_limit=np.inf, n_trees=3, n_playouts=64, variant="acp_prodigal",
+                seed=42, verbose_info=False)
+    ai.init_device_side_arrays()
+    assert np.array_equal(_streams(ai, 0, 3 * 7 * 64), om.rng_states(3 * 7 * 64, 42))
+    ocp = MCTSNC((6, 7), 7, 7, search_steps_limit=5, search_time_limit=np.inf, n_trees=3, n_playouts=64, variant="ocp_prodigal",
+                 seed=42, verbose_info=False)
+    ocp.init_device_side_arrays()
+    ref = om.rng_states(3 * 64, 42)
+    assert np.array_equal(_streams(ocp, 0, 3 * 64), ref)
+    assert np.array_equal(_streams(ocp, 1, 3), ref[[0, 64, 128]])   # tpb_e1 = 64 for Connect 4
+
+
+def test_sharded_streams_are_a_slice_of_the_global_ones():
+    kw = dict(search_steps_limit=5, search_time_limit=np.inf, n_playouts=32, variant="acp_thrifty", seed=7, verbose_info=False)
+    part = MCTSNC((6, 7), 7, 7, n_trees=2, tree_offset=4, n_trees_global=8, **kw)
+    part.init_device_side_arrays()
+    ref = om.rng_states(8 * 7 * 32, 7)
+    assert np.array_equal(_streams(part, 0, 2 * 7 * 32), ref[4 * 7 * 32:6 * 7 * 32])
+
+
+@pytest.mark.parametrize("variant", ["acp_prodigal", "ocp_thrifty"])
+def test_two_shards_equal_the_unsharded_search(variant):
+    """Root parallelism over two handles (as over two GPUs): partial sums add up to the single search with all trees."""
+    steps, T = 80, 4
+    kw = dict(search_steps_limit=steps, search_time_limit=np.inf, n_playouts=64, variant=variant, seed=5, verbose_info=False)
+    board, fills = np.zeros((6, 7), np.int8), np.zeros(7, np.int8)
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=T, n_playouts=64, variant=variant, seed=5, node_capacity=steps * 7 + 8)
+    orc.run(board, fills, 1, steps)
+    total_n, total_w = np.zeros(7, np.int64), np.zeros(7, np.int64)
+    for r in range(2):
+        shard = MCTSNC((6, 7), 7, 7, n_trees=2, tree_offset=2 * r, n_trees_global=T, **kw)
+        shard.init_device_side_arrays()
+        shard.run(board, fills, 1)
+        total_n += shard._res["actions_ns"]
+        total_w += shard._res["actions_ns_wins"]
+        assert np.array_equal(shard.export("trees_ns", max_nodes=600), orc.field("trees_ns")[2 * r:2 * r + 2, :600])
+    if "prodigal" in variant:
+        assert np.array_equal(total_n, orc.field("actions_ns")) and np.array_equal(total_w, orc.field("actions_ns_wins"))
+    else:  # thrifty: the oracle indexes by ordinal; all seven actions are expanded at the empty board
+        assert np.array_equal(total_n, orc.field("actions_ns")) and np.array_equal(total_w, orc.field("actions_ns_wins"))
+
+
+def test_time_limited_search_is_a_prefix_of_the_step_limited_one():
+    """A time budget runs the loop as several launches; the trees must equal those of one launch with as many steps."""
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=0.02, n_trees=2, n_playouts=64, variant="acp_prodigal", seed=2,
+                verbose_info=False, node_capacity=200000)
+    ai.init_device_side_arrays()
+    board, fills = np.zeros((6, 7), np.int8), np.zeros(7, np.int8)
+    best = ai.run(board, fills, 1)
+    steps = ai.steps
+    assert steps > 16          # more than one launch
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=2, n_playouts=64, variant="acp_prodigal", seed=2, node_capacity=steps * 7 + 8)
+    orc.run(board, fills, 1, steps)
+    compare_trees(ai, orc)
+    assert int(best) == orc.best_action
+    # and the forced step count of experiment replays overrides the clock (src/mctsnc.py:597-599)
+    ai.reset_random_streams()
+    ai.run(board, fills, 1, forced_search_steps_limit=25)
+    assert ai.steps == 25
+
+
+def test_info_dicts_have_the_reference_keys(capsys):
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=50, n_trees=2, n_playouts=32)
+    ai.init_device_side_arrays()
+    ai.run(np.zeros((6, 7), np.int8), np.zeros(7, np.int8), 1)
+    out = capsys.readouterr().out
+    assert "MCTSNC RUN... [MCTSNC(" in out and "MCTSNC RUN DONE. [time:" in out and "calculated max_tree_size: " in out
+    best = ai.actions_info["best"]
+    assert set(best) == {"index", "name", "n_root", "win_flag", "n", "n_wins", "q", "ucb"}
+    assert best["index"] == int(ai.best_action)
+    e = ai.actions_info[3]
+    assert abs(e["q"] - e["n_wins"] / e["n"]) < 1e-12
+    assert abs(e["ucb"] - (e["q"] + 2.0 * np.sqrt(np.log(e["n_root"]) / e["n"]))) <= 1e-6 * abs(e["ucb"])
+    perf = ai.performance_info
+    assert {"steps", "steps_per_second", "playouts", "playouts_per_second", "times_[ms]", "trees"} <= set(perf)
+    assert set(perf["times_[ms]"]) == {"total", "loop", "reduce_over_trees", "reduce_over_actions", "mean_loop", "mean_select",
+                                       "mean_expand", "mean_playout", "mean_backup"}
+    assert set(perf["trees"]) == {"count", "mean_depth", "max_depth", "mean_size", "max_size"}
+    assert perf["playouts"] == int(e["n_root"]) and perf["steps"] == 50
+
+
+def test_json_dump_has_the_reference_keys(tmp_path):
+    import json
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=30, n_trees=2, n_playouts=32, verbose_info=False)
+    ai.init_device_side_arrays()
+    ai.run(np.zeros((6, 7), np.int8), np.zeros(7, np.int8), 1)
+    ai._json_dump(str(tmp_path / "dump.json"))
+    d = json.load(open(tmp_path / "dump.json"))
+    assert {"n_trees", "n_playouts", "variant", "search_time_limit", "search_steps_limit", "ucb_c", "seed", "device_memory",
+            "trees", "trees_sizes", "trees_depths", "trees_turns", "trees_ns", "trees_ns_wins", "trees_nodes_selected",
+            "trees_selected_paths", "trees_actions_expanded", "trees_playout_outcomes",
+            "trees_playout_outcomes_children"} == set(d)
+    assert np.array(d["trees"]).shape == (2, max(d["trees_sizes"]), 8)
+
+
+def test_full_size_headline_workload_invariants():
+    """256 roots x 4 trees x 256 playouts x 2000 steps: checked through properties that hold at any size."""
+    B, steps = 256, 2000
+    boards, fills, turns = c4_random_roots(B, 20, seed=0)
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=4, n_playouts=256,
+                variant="acp_prodigal", verbose_info=False, max_batch=B)
+    ai.init_device_side_arrays()
+    out = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    again = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    for name in ("best_action", "best_n", "best_n_wins", "playouts", "plies", "actions_ns", "actions_ns_wins"):
+        assert np.array_equal(out[name], again[name]), name          # re-seeded searches repeat exactly
+    assert (out["status"] & _abi.STATUS_INTERNAL == 0).all() and (out["status"] & _abi.STATUS_TREE_FULL == 0).all()
+    assert (out["steps"] == steps).all()
+    exp = out["actions_expanded"][:, :7].astype(bool)
+    assert np.array_equal(exp, fills < 6)                              # root children = columns with room
+    root_ns = np.where(exp, out["root_ns"][:, :7], 0)
+    assert (root_ns.max(axis=1) == out["playouts"]).all()
+    assert (np.where(exp, out["actions_ns"][:, :7], 0).sum(axis=1) == out["playouts"]).all()   # every playout passes a root child
+    assert (out["actions_ns_wins"][:, :7] <= out["actions_ns"][:, :7]).all()
+    assert (out["best_n"] == np.where(out["actions_win_flags"][:, :7].any(axis=1), out["best_n"],
+                                      np.where(exp, out["actions_ns"][:, :7], -1).max(axis=1))).all()
+    for b in (0, 17, 255):                                             # tree-level invariants on a few searches
+        sizes = ai.export("trees_sizes", b)
+        smax = int(sizes.max())
+        trees, ns, wins = (ai.export(n, b, max_nodes=smax) for n in ("trees", "trees_ns", "trees_ns_wins"))
+        depths, leaves = ai.export("trees_depths", b, max_nodes=smax), ai.export("trees_leaves", b, max_nodes=smax)
+        for t in range(4):
+            n = sizes[t]
+            par = trees[t, 1:n, 0]
+            assert (par >= 0).all() and (par < np.arange(1, n)).all()
+            assert np.array_equal(depths[t, 1:n], depths[t, par] + 1)
+            child_sum = np.bincount(par, weights=ns[t, 1:n], minlength=n).astype(np.int64)
+            inner = leaves[t, :n] == 0
+            assert np.array_equal(child_sum[inner], ns[t, :n][inner].astype(np.int64))   # visits split over the children
+            win_sum = np.bincount(par, weights=wins[t, 1:n], minlength=n).astype(np.int64)
+            assert (wins[t, :n][inner] + win_sum[inner] <= ns[t, :n][inner]).all()      # the rest are draws
+            assert n == 1 + int((trees[t, :n, 1:] >= 0).sum())
+    # a search does not depend on its position in the batch
+    perm = np.random.default_rng(1).permutation(B)
+    short = ai.run_batch(boards, fills, turns, steps=100, reseed=True)
+    shuffled = ai.run_batch(boards[perm], fills[perm], turns[perm], steps=100, reseed=True)
+    assert np.array_equal(short["best_n_wins"][perm], shuffled["best_n_wins"])
+    assert np.array_equal(short["actions_ns"][perm], shuffled["actions_ns"])
+
+
+def test_ub_draws_are_replayed_like_the_oracle():
+    """A search long enough to meet draws equal to 1.0f (about 2**-25 per draw): the byte-level replay must agree."""
+    steps = 1500
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=4, n_playouts=256,
+                variant="acp_prodigal", seed=0, verbose_info=False)
+    ai.init_device_side_arrays()
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=4, n_playouts=256, variant="acp_prodigal", seed=0, node_capacity=steps * 7 + 8)
+    board, fills = np.zeros((6, 7), np.int8), np.zeros(7, np.int8)
+    ai.run(board, fills, 1)
+    orc.run(board, fills, 1, steps)
+    assert orc.ub_draws > 0 and ai._res["ub_draws"] == orc.ub_draws
+    assert ai._res["status"] & _abi.STATUS_UB_DRAW
+    compare_trees(ai, orc)
