@@ -59,7 +59,7 @@ def test_two_shards_equal_the_unsharded_search(variant):
         shard.run(board, fills, 1)
         total_n += shard._res["actions_ns"]
         total_w += shard._res["actions_ns_wins"]
-        assert np.array_equal(shard.export("trees_ns", max_nodes=600), orc.field("trees_ns")[2 * r:2 * r + 2, :600])
+        assert np.array_equal(shard.export("trees_ns", max_nodes=500), orc.field("trees_ns")[2 * r:2 * r + 2, :500])
     if "prodigal" in variant:
         assert np.array_equal(total_n, orc.field("actions_ns")) and np.array_equal(total_w, orc.field("actions_ns_wins"))
     else:  # thrifty: the oracle indexes by ordinal; all seven actions are expanded at the empty board
@@ -152,7 +152,8 @@ def test_full_size_headline_workload_invariants():
             assert np.array_equal(depths[t, 1:n], depths[t, par] + 1)
             child_sum = np.bincount(par, weights=ns[t, 1:n], minlength=n).astype(np.int64)
             inner = leaves[t, :n] == 0
-            assert np.array_equal(child_sum[inner], ns[t, :n][inner].astype(np.int64))   # visits split over the children
+            own = np.where(np.arange(n) == 0, 0, 256)     # a child got its own 256 playouts at the step that created it
+            assert np.array_equal(child_sum[inner] + own[inner], ns[t, :n][inner].astype(np.int64))   # the rest went through its children
             win_sum = np.bincount(par, weights=wins[t, 1:n], minlength=n).astype(np.int64)
             assert (wins[t, :n][inner] + win_sum[inner] <= ns[t, :n][inner]).all()      # the rest are draws
             assert n == 1 + int((trees[t, :n, 1:] >= 0).sum())
