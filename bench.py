@@ -253,8 +253,10 @@ def main():
     plies_per_launch = plies_per_pass / n_gpus
     playouts_per_launch = playouts_per_pass / n_gpus
     tree_steps_per_launch = B * args.trees * args.search_steps
-    # algorithmic HBM bytes: 32 B of stream state per playout, ~1.3 KB of tree records per tree-step
-    algo_bytes = 32.0 * playouts_per_launch + 1300.0 * tree_steps_per_launch
+    # algorithmic HBM bytes: every stream state is read and written once per launch (2 x 16 B), and a
+    # tree-step touches ~1.3 KB of tree records
+    n_streams = B * args.trees * (A if "acp" in args.variant else 1) * args.playouts
+    algo_bytes = 32.0 * n_streams + 1300.0 * tree_steps_per_launch
     hbm_achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
     peak_inst = sm_count * 4 * 32 * pk["sm_max_mhz"] * 1e6
     inst_achieved = plies_per_launch * INST_PER_PLY / (kernel_ms * 1e-3)
