@@ -164,6 +164,24 @@ int mctsnc_export_rng(mctsnc_handle *h, int32_t search, int32_t which, uint64_t 
 int mctsnc_query(mctsnc_handle *h, int32_t *threads_per_tree, int32_t *blocks_per_sm, int32_t *sm_count,
                  int64_t *bytes_allocated);
 
+/* One Connect-4 search that allocates nothing (no counterpart in the reference, whose searcher always allocates its
+   device arrays in init_device_side_arrays).  For callers that cannot allocate device memory themselves: code running
+   while a framework's caching allocator owns the device, services that forbid allocation after start-up, plug-ins that
+   are handed a stream and buffers only.  Tree pools, random streams and bookkeeping live in one fixed array inside the
+   library image (about 1.6 MB on every device that loads the library), hence the limits below; beyond them the call
+   returns MCTSNC_E_CAPACITY.
+   board/extra_info/turn: host, as for mctsnc_run.  out_device: DEVICE buffer of 3*7+4 int64 supplied by the caller:
+   root_ns[7], actions_ns[7], actions_ns_wins[7] (indexed by action), then best_action, best_win_flag, best_n, best_n_wins.
+   The result equals mctsnc_run on a freshly created handle with the same arguments.  Work is queued on `stream` and
+   not waited for, except that the first call on a device, and any call with a new (seed, n_trees, n_playouts, variant),
+   prepares the seeded streams and synchronises: make such a call before capturing the stream.  All calls share the
+   one array: it is re-initialised at the start of every call, and calls whose GPU work overlaps race on it. */
+#define MCTSNC_STATIC_MAX_TREES 4
+#define MCTSNC_STATIC_MAX_PLAYOUTS 256
+#define MCTSNC_STATIC_MAX_STEPS 512
+int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_info, int32_t turn, int32_t variant, int32_t n_trees,
+                            int32_t n_playouts, int64_t steps, float ucb_c, uint64_t seed, int64_t *out_device, void *stream);
+
 /* Text for a return code of any function above (cf. puct_cpp_cuda_error_string, src/puct/puct_gpu_v3_cpp.cu:483-485). */
 const char *mctsnc_error_string(int code);
 

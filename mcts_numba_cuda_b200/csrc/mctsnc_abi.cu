@@ -844,3 +844,168 @@ extern "C" const char *mctsnc_error_string(int code) {
     if (code > 0) return cudaGetErrorString((cudaError_t)code);
     return "mctsnc: unknown error";
 }
+
+// ===================================================================================================================
+// mctsnc_search_c4_static: one Connect-4 search that allocates nothing.
+//
+// Every other entry point works on a handle whose pools come from cudaMalloc in mctsnc_create.  Some callers cannot do
+// that: code that runs while a framework's caching allocator owns the whole device, services that forbid allocation
+// after start-up so that a search can never fail for lack of memory, plug-ins that are handed a stream and two buffers
+// and nothing else.  For them the tree pools, the random streams and the per-tree bookkeeping of this variant live in
+// one file-scope device array of fixed size (every device that loads the library carries it until the process exits),
+// so the limits below are modest.
+//
+// The array's name is only a host-side stand-in for the device object, not a device address: the first call on a device
+// (with that device current) asks the runtime for the address with cudaGetSymbolAddress and every launch gets that
+// pointer.  That first call also fills the cache of seeded streams; it synchronises, so make it before capturing a
+// stream.  All calls share the one array and it keeps what the last call left: what has to start from zero is
+// cleared on the caller's stream at the start of every call, and two calls whose work overlaps on the GPU (different
+// streams, different host threads) would race on it -- run them one after the other.
+namespace {
+namespace fixed {
+
+constexpr int MAX_TREES = MCTSNC_STATIC_MAX_TREES;
+constexpr int MAX_PLAYOUTS = MCTSNC_STATIC_MAX_PLAYOUTS;
+constexpr int MAX_STEPS = MCTSNC_STATIC_MAX_STEPS;
+constexpr int A = c4::A;
+constexpr long long CAP = (long long)MAX_STEPS * A + 1 + A;   // nodes per tree
+constexpr int MAX_STREAMS = MAX_TREES * A * MAX_PLAYOUTS;
+constexpr int MAX_DEVICES = 64;
+
+struct Scratch {
+    int4 rec[MAX_TREES * CAP];
+    ulonglong2 board[MAX_TREES * CAP];
+    ulonglong2 rng[MAX_STREAMS];
+    ulonglong2 rng_base[MAX_STREAMS];
+    ulonglong2 rng_expand[MAX_TREES];
+    ulonglong2 rng_expand_base[MAX_TREES];
+    ulonglong2 root_board[1];
+    long long sums[3 * A];
+    DevResult dres[1];
+    TreeState state[MAX_TREES];
+    int parent[MAX_TREES * CAP];
+    int paths[MAX_TREES * PATH_CAP];
+    int child_out[MAX_TREES * A * 2];
+    short actions_expanded[MAX_TREES * (A + 2)];
+    unsigned char flags[2 * A];
+    signed char root_turn[16];
+};
+
+static __device__ __align__(256) unsigned char g_static_scratch[sizeof(Scratch)];
+
+struct DeviceSetup {
+    Scratch *ptr = nullptr;       // device address of g_static_scratch on this device
+    bool streams_cached = false;  // rng_base / rng_expand_base hold the streams of the key below
+    unsigned long long seed = 0;
+    int n_trees = 0, n_playouts = 0, ocp = 0;
+};
+DeviceSetup g_setup[MAX_DEVICES];
+ulonglong2 g_host_streams[MAX_STREAMS];   // staging for the seeded streams (static: no host allocation either)
+
+__global__ void copy_streams_kernel(ulonglong2 *dst, const ulonglong2 *src, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// [root_ns | actions_ns | actions_ns_wins] are already in `out`; append best action, win flag, n, n_wins
+__global__ void append_best_kernel(const DevResult *dres, long long *out, int A_) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        out[3 * A_ + 0] = dres->best_action;
+        out[3 * A_ + 1] = dres->best_win_flag;
+        out[3 * A_ + 2] = dres->best_n;
+        out[3 * A_ + 3] = dres->best_n_wins;
+    }
+}
+
+}  // namespace fixed
+}  // namespace
+
+extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_info, int32_t turn, int32_t variant,
+                                       int32_t n_trees, int32_t n_playouts, int64_t steps, float ucb_c, uint64_t seed,
+                                       int64_t *out_device, void *stream) {
+    using namespace fixed;
+    if (!board || !out_device || (turn != 1 && turn != -1) || variant < 0 || variant > 3 || n_trees < 1 || n_playouts < 1 ||
+        (n_playouts & (n_playouts - 1)) != 0 || steps < 0 || !(ucb_c >= 0.f))
+        return MCTSNC_E_BAD_ARGUMENT;
+    if (n_trees > MAX_TREES || n_playouts > MAX_PLAYOUTS || steps > MAX_STEPS) return MCTSNC_E_CAPACITY;
+    int device = -1;
+    CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= MAX_DEVICES) return MCTSNC_E_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    DeviceSetup &su = g_setup[device];
+    if (!su.ptr) {
+        // once per device, with that device current: the device address behind the symbol
+        void *p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        su.ptr = reinterpret_cast<Scratch *>(p);
+        su.streams_cached = false;
+    }
+    Scratch *sc = su.ptr;
+    ulonglong2 root;
+    int rc = c4_encode_root(board, extra_info, &root);
+    if (rc) return rc;
+    const bool ocp = variant == MCTSNC_OCP_THRIFTY || variant == MCTSNC_OCP_PRODIGAL;
+    const int per_tree = ocp ? n_playouts : A * n_playouts;
+    const int n_streams = n_trees * per_tree;
+    if (!su.streams_cached || su.seed != seed || su.n_trees != n_trees || su.n_playouts != n_playouts || su.ocp != (int)ocp) {
+        // seeded streams of this configuration (numba's create_xoroshiro128p_states): computed on the host into a
+        // static buffer and kept on the device for the calls to come
+        su.streams_cached = false;
+        CUDA_TRY(cudaStreamSynchronize(s));  // the staging buffer is reused: nothing may still be reading it
+        make_streams(seed, 0, n_streams, 1, g_host_streams);
+        CUDA_TRY(cudaMemcpyAsync(sc->rng_base, g_host_streams, sizeof(ulonglong2) * n_streams, cudaMemcpyHostToDevice, s));
+        CUDA_TRY(cudaStreamSynchronize(s));
+        if (ocp) {
+            const int tpb_e1 = 64;  // Connect 4: min(max(pow2(42), pow2(7)), 512), src/mctsnc.py:360-365
+            make_streams(seed, 0, n_trees, tpb_e1, g_host_streams);
+            CUDA_TRY(cudaMemcpyAsync(sc->rng_expand_base, g_host_streams, sizeof(ulonglong2) * n_trees, cudaMemcpyHostToDevice, s));
+            CUDA_TRY(cudaStreamSynchronize(s));
+        }
+        su.seed = seed;
+        su.n_trees = n_trees;
+        su.n_playouts = n_playouts;
+        su.ocp = (int)ocp;
+        su.streams_cached = true;
+    }
+    // what has to start from zero, and the root (17 bytes from the stack: staged by the runtime before it returns)
+    CUDA_TRY(cudaMemsetAsync(sc->state, 0, sizeof(sc->state), s));
+    CUDA_TRY(cudaMemsetAsync(sc->child_out, 0, sizeof(sc->child_out), s));
+    CUDA_TRY(cudaMemsetAsync(sc->actions_expanded, 0, sizeof(sc->actions_expanded), s));
+    const signed char t8 = (signed char)turn;
+    CUDA_TRY(cudaMemcpyAsync(sc->root_board, &root, sizeof(root), cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpyAsync(sc->root_turn, &t8, 1, cudaMemcpyHostToDevice, s));
+    copy_streams_kernel<<<32, 256, 0, s>>>(sc->rng, sc->rng_base, n_streams);
+    if (ocp) copy_streams_kernel<<<1, 32, 0, s>>>(sc->rng_expand, sc->rng_expand_base, n_trees);
+    SearchParams p;
+    p.rec = sc->rec;
+    p.board = sc->board;
+    p.parent = sc->parent;
+    p.state = sc->state;
+    p.paths = sc->paths;
+    p.actions_expanded = sc->actions_expanded;
+    p.child_out = sc->child_out;
+    p.rng_playout = sc->rng;
+    p.rng_expand = sc->rng_expand;
+    p.root_board = sc->root_board;
+    p.root_turn = sc->root_turn;
+    p.cap = CAP;
+    p.node_limit = CAP;
+    p.n_trees = n_trees;
+    p.n_playouts = n_playouts;
+    p.log2_playouts = 0;
+    while ((1 << p.log2_playouts) < n_playouts) p.log2_playouts++;
+    p.n_actions = A;
+    p.variant = variant;
+    p.steps = (int)steps;
+    p.first = 1;
+    p.ucb_c = ucb_c;
+    const size_t dyn_smem = sizeof(ulonglong2) * (size_t)per_tree;   // <= 28 KB: below the 48 KB that need an opt-in
+    if (ocp) c4::search_kernel<true><<<n_trees, 256, dyn_smem, s>>>(p);
+    else c4::search_kernel<false><<<n_trees, 256, dyn_smem, s>>>(p);
+    CUDA_TRY(cudaGetLastError());
+    long long *out = reinterpret_cast<long long *>(out_device);
+    reduce_over_trees_kernel<<<1, 256, 0, s>>>(sc->rec, sc->state, CAP, n_trees, A, out, sc->flags, sc->dres);
+    const bool thrifty = variant == MCTSNC_OCP_THRIFTY || variant == MCTSNC_ACP_THRIFTY;
+    reduce_over_actions_kernel<<<1, 8, 0, s>>>(out, sc->flags, A, 8, thrifty ? 1 : 0, sc->dres);
+    append_best_kernel<<<1, 32, 0, s>>>(sc->dres, out, A);
+    return (int)cudaGetLastError();
+}

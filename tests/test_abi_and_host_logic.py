@@ -18,7 +18,7 @@ def declared_functions():
     with open(os.path.join(ROOT, "include", "mctsnc_b200.h")) as f:
         text = f.read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mctsnc_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(mctsnc_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
