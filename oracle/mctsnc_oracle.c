@@ -496,8 +496,13 @@ static int playout_thread(mo_ctx *c, playout_local *L, int ti, int32_t node, int
     memset(L->legal, 0, sizeof(L->legal)); /* convention: a fresh local array reads as zeros */
     int turn = NODE(c, trees_turns, ti, node);
     int outcome = last_action != -1 ? compute_outcome(c, L->board, L->extra, turn, last_action) : 2;
-    for (;;) {
+    for (int guard = 0;; guard++) {
         if (outcome == -1 || outcome == 0 || outcome == 1) return outcome;
+        if (guard >= 4096) { /* only reachable after a 1.0f draw has put list and board out of step (the reference
+                                would loop on); the CUDA replay gives up at the same point with the same answer */
+            c->error |= 16;
+            return 0;
+        }
         legal_actions_playout(c, L->board, L->extra, L->legal);
         int count = L->legal[LEGAL_LEN - 1];
         /* :1882 -- float32 * int16 is a float32 product, then int16() truncation */
@@ -875,3 +880,26 @@ int mo_best_win_flag(mo_ctx *c) { return c->best_win_flag; }
 int64_t mo_best_n(mo_ctx *c) { return c->best_n; }
 int64_t mo_best_n_wins(mo_ctx *c) { return c->best_n_wins; }
 int mo_tpb_e1(mo_ctx *c) { return c->tpb_e1; }
+
+/* ------------------------------------------------------------------------- */
+/* game mechanics alone, for the tests that pin them to the reference's CPU classes (src/c4.py, src/gomoku.py):
+   plays `n_actions` actions from the empty board with take_action, first player +1 (src/mcts.py:63), and writes the
+   value of compute_outcome after every action (2 = game ongoing) */
+int mo_replay_game(int game, int m, int n, const int16_t *actions, int n_actions, int8_t *outcomes, int8_t *final_board) {
+    mo_ctx c;
+    memset(&c, 0, sizeof(c));
+    c.game = game; c.m = m; c.n = n; c.extra = game == GAME_C4 ? n : 1; c.A = game == GAME_C4 ? n : m * n;
+    int8_t board[32 * 32];
+    int8_t extra[64];
+    memset(board, 0, sizeof(board));
+    memset(extra, 0, sizeof(extra));
+    int turn = 1;
+    for (int k = 0; k < n_actions; k++) {
+        if (!is_action_legal(&c, board, extra, actions[k])) return -(k + 1);
+        take_action(&c, board, extra, turn, actions[k]);
+        turn = -turn;
+        outcomes[k] = (int8_t)compute_outcome(&c, board, extra, turn, actions[k]);
+    }
+    memcpy(final_board, board, (size_t)m * n);
+    return c.error;
+}

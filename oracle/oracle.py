@@ -84,6 +84,9 @@ def lib():
         L.mo_rng_uniform_f32.argtypes = [ctypes.c_void_p]
         L.mo_rng_next.restype = ctypes.c_uint64
         L.mo_rng_next.argtypes = [ctypes.c_void_p]
+        L.mo_replay_game.restype = ctypes.c_int
+        L.mo_replay_game.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                     ctypes.c_void_p, ctypes.c_void_p]
         _lib = L
     return _lib
 
@@ -105,6 +108,18 @@ def rng_states(n, seed):
     out = np.zeros((n, 2), dtype=np.uint64)
     lib().mo_rng_init_states(out.ctypes.data, n, ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF))
     return out
+
+
+def replay_game(game, m, n, actions):
+    """Plays `actions` from the empty board with the oracle's game mechanics; returns (outcomes after every action,
+    final board).  Outcome 2 means "game goes on"."""
+    actions = np.ascontiguousarray(actions, dtype=np.int16)
+    outcomes = np.zeros(len(actions), dtype=np.int8)
+    board = np.zeros((m, n), dtype=np.int8)
+    rc = lib().mo_replay_game(game, m, n, actions.ctypes.data, len(actions), outcomes.ctypes.data, board.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"oracle replay failed with {rc}")
+    return outcomes, board
 
 
 class OracleMCTSNC:
