@@ -14,6 +14,7 @@
 
 #include "c4_search.cuh"
 #include "common.cuh"
+#include "gomoku_search.cuh"
 #include "rng.cuh"
 
 using namespace mctsnc;
@@ -78,6 +79,14 @@ struct mctsnc_handle {
     ulonglong2 *rng_expand_base = nullptr;
     ulonglong2 *root_board = nullptr;
     signed char *root_turn = nullptr;
+    // Gomoku only
+    unsigned *gboard = nullptr;           // [trees][cap][16]
+    gomoku::StepInfo *gstep = nullptr;    // [trees]
+    int *path_ns = nullptr, *path_wins = nullptr;
+    signed char *child_outcome = nullptr;
+    unsigned char *child_action = nullptr;
+    unsigned *root_gboard = nullptr;      // [max_batch][16]
+    unsigned *h_root_gboard = nullptr;
     long long *sums = nullptr;            // [max_batch][3A]
     unsigned char *flags = nullptr;       // [max_batch][2A]: win flags, expanded-at-root
     DevResult *dres = nullptr;            // [max_batch]
@@ -252,6 +261,106 @@ __global__ void reduce_over_actions_kernel(const long long *sums, const unsigned
     }
 }
 
+// _reduce_over_trees_* for Gomoku nodes (first child + number of children; the child of action a is found through the
+// empty cells of the root position)
+__global__ void gomoku_reduce_over_trees_kernel(const int4 *rec, const unsigned *board, const TreeState *state, long long cap,
+                                                int n_trees, long long *sums, unsigned char *flags, DevResult *dres) {
+    constexpr int A = gomoku::A;
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int4 *r0 = rec + (long long)b * n_trees * cap;
+    const unsigned *b0 = board + (long long)b * n_trees * cap * 16;   // root position (the same in every tree)
+    __shared__ unsigned s_empty[8];
+    __shared__ int s_prefix[9];
+    if (tid < 8) s_empty[tid] = ~(b0[tid] | b0[8 + tid]) & (tid == 7 ? 0x1u : 0xFFFFFFFFu);
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int w = 0; w < 8; w++) {
+            s_prefix[w] = acc;
+            acc += __popc(s_empty[w]);
+        }
+        s_prefix[8] = acc;
+    }
+    __syncthreads();
+    const int root_turn = gomoku::g_turn(r0[0].w);
+    const int n_children0 = r0[0].w & gomoku::G_NCHILD_MASK;
+    for (int a = tid; a < A; a += blockDim.x) {
+        long long s_root = 0, s_n = 0, s_w = 0;
+        unsigned char win = 0;
+        const int w = a >> 5, bit = a & 31;
+        const int rank = s_prefix[w] + __popc(s_empty[w] & ((1u << bit) - 1u));
+        const bool expanded = ((s_empty[w] >> bit) & 1u) && rank < n_children0;
+        if (expanded) {
+            for (int t = 0; t < n_trees; t++) {
+                const int4 *rt = r0 + (long long)t * cap;
+                const int4 root = rt[0];
+                s_root += root.x;
+                if (rank < (root.w & gomoku::G_NCHILD_MASK)) {
+                    const int4 c = rt[root.z + rank];
+                    s_n += c.x;
+                    s_w += c.y;
+                    if (t == 0) win = (c.w & gomoku::G_TERMINAL) && gomoku::g_outcome(c.w) == root_turn;
+                }
+            }
+        }
+        sums[(long long)b * 3 * A + a] = s_root;
+        sums[(long long)b * 3 * A + A + a] = s_n;
+        sums[(long long)b * 3 * A + 2 * A + a] = s_w;
+        flags[(long long)b * 2 * A + a] = win;
+        flags[(long long)b * 2 * A + A + a] = expanded;
+    }
+    __shared__ long long sh_depth[256];
+    __shared__ int sh_maxd[256];
+    long long dsum = 0;
+    int dmax = 0;
+    for (int t = 0; t < n_trees; t++) {
+        const int size = state[b * n_trees + t].size;
+        const int4 *rt = r0 + (long long)t * cap;
+        for (int i = tid; i < size; i += blockDim.x) {
+            const int d = meta_depth(rt[i].w);
+            dsum += d;
+            dmax = d > dmax ? d : dmax;
+        }
+    }
+    sh_depth[tid] = dsum;
+    sh_maxd[tid] = dmax;
+    __syncthreads();
+    for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+        if (tid < s) {
+            sh_depth[tid] += sh_depth[tid + s];
+            sh_maxd[tid] = max(sh_maxd[tid], sh_maxd[tid + s]);
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        DevResult d;
+        d.best_action = -1;
+        d.best_win_flag = 0;
+        d.best_n = 0;
+        d.best_n_wins = 0;
+        d.playouts = 0;
+        d.plies = 0;
+        d.ub_draws = 0;
+        d.status = 0;
+        d.max_size = 0;
+        d.total_nodes = 0;
+        for (int t = 0; t < n_trees; t++) {
+            const TreeState &ts = state[b * n_trees + t];
+            d.playouts += r0[(long long)t * cap].x;
+            d.plies += (long long)ts.plies;
+            d.ub_draws += (long long)ts.ub_draws;
+            d.status |= ts.status;
+            d.total_nodes += ts.size;
+            d.max_size = ts.size > d.max_size ? ts.size : d.max_size;
+        }
+        d.n_root_actions = n_children0;
+        d.max_depth = sh_maxd[0];
+        d.depth_sum = sh_depth[0];
+        dres[b] = d;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // host helpers
 
@@ -300,6 +409,20 @@ int c4_encode_root(const int8_t *board, const int8_t *fills, ulonglong2 *out) {
     return 0;
 }
 
+// int8 board -> two 225-bit stone sets (cell (i, j) = bit i*15+j)
+int gomoku_encode_root(const int8_t *board, unsigned *out) {
+    for (int k = 0; k < 16; k++) out[k] = 0;
+    for (int c = 0; c < gomoku::A; c++) {
+        const int v = board[c];
+        if (v == -1) out[c >> 5] |= 1u << (c & 31);
+        else if (v == 1) out[8 + (c >> 5)] |= 1u << (c & 31);
+        else if (v != 0) return MCTSNC_E_BAD_ROOT;
+    }
+    return 0;
+}
+
+bool is_gomoku(const mctsnc_config &c) { return c.game == MCTSNC_GAME_GOMOKU; }
+
 template <typename T>
 int dev_alloc(mctsnc_handle *h, T **p, long long n) {
     if (n <= 0) n = 1;
@@ -327,6 +450,14 @@ void release(mctsnc_handle *h) {
     cudaFree(h->rng_expand_base);
     cudaFree(h->root_board);
     cudaFree(h->root_turn);
+    cudaFree(h->gboard);
+    cudaFree(h->gstep);
+    cudaFree(h->path_ns);
+    cudaFree(h->path_wins);
+    cudaFree(h->child_outcome);
+    cudaFree(h->child_action);
+    cudaFree(h->root_gboard);
+    cudaFreeHost(h->h_root_gboard);
     cudaFree(h->sums);
     cudaFree(h->flags);
     cudaFree(h->dres);
@@ -374,6 +505,17 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
                 cudaStream_t stream) {
     const int cells = h->cfg.board_rows * h->cfg.board_cols;
     const int extra = h->cfg.extra_info_memory;
+    if (is_gomoku(h->cfg)) {
+        for (int b = 0; b < batch; b++) {
+            if (turns[b] != 1 && turns[b] != -1) return MCTSNC_E_BAD_ARGUMENT;
+            const int rc = gomoku_encode_root(boards + (long long)b * cells, h->h_root_gboard + (long long)b * 16);
+            if (rc) return rc;
+            h->h_root_turn[b] = turns[b];
+        }
+        CUDA_TRY(cudaMemcpyAsync(h->root_gboard, h->h_root_gboard, sizeof(unsigned) * 16 * batch, cudaMemcpyHostToDevice, stream));
+        CUDA_TRY(cudaMemcpyAsync(h->root_turn, h->h_root_turn, batch, cudaMemcpyHostToDevice, stream));
+        return 0;
+    }
     for (int b = 0; b < batch; b++) {
         if (turns[b] != 1 && turns[b] != -1) return MCTSNC_E_BAD_ARGUMENT;
         const int rc = c4_encode_root(boards + (long long)b * cells, extras ? extras + (long long)b * extra : nullptr,
@@ -386,7 +528,50 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
     return 0;
 }
 
+// Gomoku: two launches per step (tree step, playouts) and a closing backup, all enqueued without waiting
+int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cudaStream_t stream) {
+    gomoku::Params p;
+    p.rec = h->rec;
+    p.board = h->gboard;
+    p.parent = h->parent;
+    p.state = h->state;
+    p.step = h->gstep;
+    p.paths = h->paths;
+    p.path_ns = h->path_ns;
+    p.path_wins = h->path_wins;
+    p.actions_expanded = h->actions_expanded;
+    p.child_out = h->child_out;
+    p.child_outcome = h->child_outcome;
+    p.child_action = h->child_action;
+    p.rng_playout = h->rng_playout;
+    p.rng_expand = h->rng_expand;
+    p.root_board = h->root_gboard;
+    p.root_turn = h->root_turn;
+    p.cap = h->cfg.node_capacity;
+    p.node_limit = h->cfg.max_tree_size < h->cfg.node_capacity ? h->cfg.max_tree_size : h->cfg.node_capacity;
+    p.n_trees = h->cfg.n_trees;
+    p.n_playouts = h->cfg.n_playouts;
+    p.variant = h->cfg.variant;
+    p.ucb_c = h->cfg.ucb_c;
+    const unsigned trees = (unsigned)((long long)batch * h->cfg.n_trees);
+    const bool ocp = is_ocp(h->cfg);
+    const int P = h->cfg.n_playouts;
+    const dim3 pgrid(gomoku::A, trees);
+    h->threads = 256;
+    for (int s = 0; s <= steps; s++) {
+        p.first = (first && s == 0) ? 1 : 0;
+        p.backup_only = s == steps ? 1 : 0;
+        if (ocp) gomoku::tree_step_kernel<true><<<trees, 256, 0, stream>>>(p);
+        else gomoku::tree_step_kernel<false><<<trees, 256, 0, stream>>>(p);
+        if (s == steps) break;
+        if (ocp) gomoku::playout_kernel<true><<<pgrid, P, h->dyn_smem, stream>>>(p);
+        else gomoku::playout_kernel<false><<<pgrid, P, h->dyn_smem, stream>>>(p);
+    }
+    return (int)cudaGetLastError();
+}
+
 int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_t stream) {
+    if (is_gomoku(h->cfg)) return launch_search_gomoku(h, batch, steps, first, stream);
     SearchParams p;
     p.rec = h->rec;
     p.board = h->board;
@@ -419,6 +604,11 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
 }
 
 int launch_reduce_trees(mctsnc_handle *h, int batch, long long *sums, cudaStream_t stream) {
+    if (is_gomoku(h->cfg)) {
+        gomoku_reduce_over_trees_kernel<<<batch, 256, 0, stream>>>(h->rec, h->gboard, h->state, h->cfg.node_capacity,
+                                                                  h->cfg.n_trees, sums, h->flags, h->dres);
+        return (int)cudaGetLastError();
+    }
     reduce_over_trees_kernel<<<batch, 256, 0, stream>>>(h->rec, h->state, h->cfg.node_capacity, h->cfg.n_trees, h->A, sums,
                                                         h->flags, h->dres);
     return (int)cudaGetLastError();
@@ -482,9 +672,16 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
         return MCTSNC_E_BAD_ARGUMENT;
     if (c.threads_per_tree != 0 && (c.threads_per_tree < 32 || c.threads_per_tree > 1024 || c.threads_per_tree % 32))
         return MCTSNC_E_BAD_ARGUMENT;
-    if (c.game != MCTSNC_GAME_C4) return MCTSNC_E_UNSUPPORTED;
-    if (c.board_rows != c4::ROWS || c.board_cols != c4::COLS || c.max_actions != c4::A || c.extra_info_memory != c4::COLS)
+    if (c.game == MCTSNC_GAME_C4) {
+        if (c.board_rows != c4::ROWS || c.board_cols != c4::COLS || c.max_actions != c4::A || c.extra_info_memory != c4::COLS)
+            return MCTSNC_E_UNSUPPORTED;
+    } else if (c.game == MCTSNC_GAME_GOMOKU) {
+        if (c.board_rows != gomoku::M || c.board_cols != gomoku::N || c.max_actions != gomoku::A || c.extra_info_memory > 1 ||
+            c.n_playouts < 32)
+            return MCTSNC_E_UNSUPPORTED;
+    } else {
         return MCTSNC_E_UNSUPPORTED;
+    }
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) {
         cudaGetLastError();
@@ -515,8 +712,11 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     const bool ocp = is_ocp(c);
     h->rng_per_search = ocp ? (long long)c.n_trees * c.n_playouts : (long long)c.n_trees * h->A * c.n_playouts;
     h->dyn_smem = sizeof(ulonglong2) * (size_t)(h->rng_per_search / c.n_trees);
+    if (is_gomoku(c)) h->dyn_smem = sizeof(unsigned) * (size_t)gomoku::THREAD_WORDS * c.n_playouts;   // per-thread game state
     if (h->dyn_smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(search_kernel_ptr(c), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
+        const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_kernel<true> : (const void *)gomoku::playout_kernel<false>)
+                                          : search_kernel_ptr(c);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
         if (e != cudaSuccess) {
             delete h;
             return (int)e;
@@ -524,7 +724,16 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     }
     int rc = 0;
     if (!rc) rc = dev_alloc(h, &h->rec, nodes);
-    if (!rc) rc = dev_alloc(h, &h->board, nodes);
+    if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->board, nodes);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->gboard, nodes * 16);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->gstep, h->n_trees_total);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->path_ns, h->n_trees_total * PATH_CAP);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->path_wins, h->n_trees_total * PATH_CAP);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->child_outcome, h->n_trees_total * h->A);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->child_action, h->n_trees_total * h->A);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->root_gboard, (long long)c.max_batch * 16);
+    if (!rc && is_gomoku(c) && cudaMallocHost((void **)&h->h_root_gboard, sizeof(unsigned) * 16 * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && is_gomoku(c)) rc = (int)cudaMemset(h->gstep, 0, sizeof(gomoku::StepInfo) * h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->parent, nodes);
     if (!rc) rc = dev_alloc(h, &h->state, h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->paths, h->n_trees_total * PATH_CAP);
@@ -698,6 +907,67 @@ extern "C" int mctsnc_run_batch(mctsnc_handle *h, int32_t batch, const int8_t *b
     return mctsnc_finish_batch_device(h, batch, nullptr, results, nullptr);
 }
 
+// per-node fields of Gomoku trees in the reference's formats (see mctsnc_export)
+static int export_nodes_gomoku(mctsnc_handle *h, const std::vector<TreeState> &st, long long g0, int field, void *dst,
+                               long long max_nodes) {
+    constexpr int A = gomoku::A;
+    const int T = h->cfg.n_trees;
+    const long long cap = h->cfg.node_capacity;
+    const int extra = h->cfg.extra_info_memory < 1 ? 1 : h->cfg.extra_info_memory;
+    std::vector<int4> rec;
+    std::vector<unsigned> brd;
+    std::vector<int> par;
+    for (int t = 0; t < T; t++) {
+        long long n = st[t].size < max_nodes ? st[t].size : max_nodes;
+        if (n > cap) n = cap;
+        rec.resize((size_t)n);
+        CUDA_TRY(cudaMemcpy(rec.data(), h->rec + (g0 + t) * cap, sizeof(int4) * n, cudaMemcpyDeviceToHost));
+        if (field == MCTSNC_F_TREES) {
+            par.resize((size_t)n);
+            CUDA_TRY(cudaMemcpy(par.data(), h->parent + (g0 + t) * cap, sizeof(int) * n, cudaMemcpyDeviceToHost));
+        }
+        if (field == MCTSNC_F_TREES || field == MCTSNC_F_BOARDS) {
+            brd.resize((size_t)n * 16);
+            CUDA_TRY(cudaMemcpy(brd.data(), h->gboard + (g0 + t) * cap * 16, sizeof(unsigned) * 16 * n, cudaMemcpyDeviceToHost));
+        }
+        for (long long i = 0; i < max_nodes; i++) {
+            const bool valid = i < n;
+            const int4 r = valid ? rec[(size_t)i] : make_int4(0, 0, -1, 0);
+            const long long o = (long long)t * max_nodes + i;
+            const unsigned *b = valid && !brd.empty() ? &brd[(size_t)i * 16] : nullptr;
+            switch (field) {
+            case MCTSNC_F_TREES: {
+                int32_t *row = (int32_t *)dst + o * (1 + A);
+                row[0] = valid ? par[(size_t)i] : -1;
+                const int n_children = r.w & gomoku::G_NCHILD_MASK;
+                int rank = 0;
+                for (int a = 0; a < A; a++) {
+                    const bool empty = valid && !(((b[a >> 5] | b[8 + (a >> 5)]) >> (a & 31)) & 1u);
+                    row[1 + a] = (empty && rank < n_children) ? r.z + rank : -1;
+                    rank += empty;
+                }
+                break;
+            }
+            case MCTSNC_F_DEPTHS: ((int16_t *)dst)[o] = valid ? (int16_t)meta_depth(r.w) : 0; break;
+            case MCTSNC_F_TURNS: ((int8_t *)dst)[o] = valid ? (int8_t)gomoku::g_turn(r.w) : 0; break;
+            case MCTSNC_F_LEAVES: ((uint8_t *)dst)[o] = valid ? ((r.w & gomoku::G_NCHILD_MASK) == 0) : 0; break;
+            case MCTSNC_F_TERMINALS: ((uint8_t *)dst)[o] = valid ? ((r.w & gomoku::G_TERMINAL) != 0) : 0; break;
+            case MCTSNC_F_OUTCOMES: ((int8_t *)dst)[o] = valid ? (int8_t)gomoku::g_outcome(r.w) : 0; break;
+            case MCTSNC_F_NS: ((int32_t *)dst)[o] = valid ? r.x : 0; break;
+            case MCTSNC_F_NS_WINS: ((int32_t *)dst)[o] = valid ? r.y : 0; break;
+            case MCTSNC_F_BOARDS: {
+                int8_t *bo = (int8_t *)dst + o * A;
+                for (int a = 0; a < A; a++)
+                    bo[a] = !valid ? 0 : (((b[8 + (a >> 5)] >> (a & 31)) & 1u) ? 1 : (((b[a >> 5] >> (a & 31)) & 1u) ? -1 : 0));
+                break;
+            }
+            case MCTSNC_F_EXTRA_INFOS: memset((int8_t *)dst + o * extra, 0, extra); break;
+            }
+        }
+    }
+    return 0;
+}
+
 extern "C" int mctsnc_export(mctsnc_handle *h, int32_t search, int32_t field, void *dst, int64_t max_nodes) {
     if (!h || !dst || search < 0 || search >= h->cfg.max_batch) return MCTSNC_E_BAD_ARGUMENT;
     CUDA_TRY(cudaSetDevice(h->cfg.device));
@@ -741,6 +1011,7 @@ extern "C" int mctsnc_export(mctsnc_handle *h, int32_t search, int32_t field, vo
         break;
     }
     if (field < 0 || field > MCTSNC_F_EXTRA_INFOS || max_nodes < 1) return MCTSNC_E_BAD_ARGUMENT;
+    if (is_gomoku(h->cfg)) return export_nodes_gomoku(h, st, g0, field, dst, max_nodes);
     const int cells = h->cfg.board_rows * h->cfg.board_cols;
     const int extra = h->cfg.extra_info_memory;
     std::vector<int4> rec;

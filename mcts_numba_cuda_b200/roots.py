@@ -54,3 +54,45 @@ def c4_random_roots(count, max_plies, seed, first_turn=1):
         boards[r], fills[r], turns[r] = board, fill, turn
         r += 1
     return boards, fills, turns
+
+
+def _gomoku_five(board, i, j):
+    m, n = board.shape
+    token = board[i, j]
+    for di, dj in ((1, 0), (0, 1), (1, 1), (1, -1)):
+        total = 0
+        for sign in (1, -1):
+            for k in range(1, 6):
+                ii, jj = i + sign * k * di, j + sign * k * dj
+                if not (0 <= ii < m and 0 <= jj < n) or board[ii, jj] != token:
+                    break
+                total += 1
+        if total == 4:
+            return True
+    return False
+
+
+def gomoku_random_roots(count, max_plies, seed, first_turn=1, size=15):
+    """Returns (boards int8[count,15,15], turns int8[count]); Gomoku has no extra information."""
+    rng = np.random.default_rng(seed)
+    boards = np.zeros((count, size, size), dtype=np.int8)
+    turns = np.zeros(count, dtype=np.int8)
+    r = 0
+    while r < count:
+        k = int(rng.integers(0, max_plies + 1))
+        board = np.zeros((size, size), dtype=np.int8)
+        turn = first_turn
+        ok = True
+        for _ in range(k):
+            empty = np.flatnonzero(board == 0)
+            a = int(rng.choice(empty))
+            board[a // size, a % size] = turn
+            if _gomoku_five(board, a // size, a % size):
+                ok = False
+                break
+            turn = -turn
+        if not ok or not (board == 0).any():
+            continue
+        boards[r], turns[r] = board, turn
+        r += 1
+    return boards, turns
