@@ -26,8 +26,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-A = 7
-INST_PER_PLY = 65.0  # thread instructions of one playout ply in the bitboard formulation (yardstick)
+GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0, "name": "Connect-4 6x7"},
+         "gomoku": {"shape": (15, 15), "extra": 0, "actions": 225, "inst_per_ply": 100.0, "name": "Gomoku 15x15"}}
+# inst_per_ply: thread instructions of one playout ply (yardstick of the issue roofline)
 
 
 def parse_args():
@@ -36,6 +37,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--game", default="c4", choices=sorted(GAMES))
     ap.add_argument("--roots", type=int, default=256)
     ap.add_argument("--search-steps", type=int, default=2000)
     ap.add_argument("--trees", type=int, default=4)
@@ -106,15 +108,19 @@ class ClockSampler:
 
 
 def make_roots(args):
-    from mcts_numba_cuda_b200.roots import c4_random_roots
+    from mcts_numba_cuda_b200.roots import c4_random_roots, gomoku_random_roots
+    if args.game == "gomoku":
+        boards, turns = gomoku_random_roots(args.roots, args.max_plies, seed=0)
+        return boards, None, turns
     return c4_random_roots(args.roots, args.max_plies, seed=0)
 
 
 def oracle_search(job):
     from oracle.oracle import OracleMCTSNC
-    board, fills, turn, trees, playouts, variant, steps = job
-    o = OracleMCTSNC((6, 7), 7, 7, n_trees=trees, n_playouts=playouts, variant=variant, seed=0,
-                     node_capacity=steps * A + 8)
+    board, fills, turn, trees, playouts, variant, steps, game = job
+    G = GAMES[game]
+    o = OracleMCTSNC(G["shape"], G["extra"], G["actions"], n_trees=trees, n_playouts=playouts, variant=variant, seed=0,
+                     device_memory=16.0 if game == "gomoku" else 2.0, node_capacity=steps * G["actions"] + G["actions"] + 8)
     t0 = time.perf_counter()
     o.run(board, fills, int(turn), steps)
     return o.playouts, o.plies, time.perf_counter() - t0
@@ -125,8 +131,8 @@ def cpu_port_baseline(args, boards, fills, turns, threads, n_roots, steps):
     from concurrent.futures import ThreadPoolExecutor
     from oracle import oracle as om
     om.lib()
-    jobs = [(boards[i % len(boards)], fills[i % len(boards)], turns[i % len(boards)], args.trees, args.playouts,
-             args.variant, steps) for i in range(n_roots)]
+    jobs = [(boards[i % len(boards)], fills[i % len(boards)] if fills is not None else None, turns[i % len(boards)],
+             args.trees, args.playouts, args.variant, steps, args.game) for i in range(n_roots)]
     t0 = time.perf_counter()
     with ThreadPoolExecutor(max_workers=threads) as ex:
         res = list(ex.map(oracle_search, jobs))
@@ -137,7 +143,7 @@ def cpu_port_baseline(args, boards, fills, turns, threads, n_roots, steps):
 
 
 def config_dict(args, n_gpus):
-    return {"workload": f"Connect-4 6x7 {args.variant}, n_trees={args.trees} per GPU, n_playouts={args.playouts}, "
+    return {"workload": f"{GAMES[args.game]['name']} {args.variant}, n_trees={args.trees} per GPU, n_playouts={args.playouts}, "
                         f"search_steps={args.search_steps}, {args.roots} seeded random roots (0..{args.max_plies} plies) per pass",
             "trees_per_search_total": args.trees * n_gpus, "parallelism": f"root-parallel x{n_gpus}" if n_gpus > 1 else "single GPU",
             "l2": "no flush: the tree pools of one pass (~0.5 GB) exceed the 126 MB L2", "seed": 0, "ucb_c": 2.0}
@@ -188,9 +194,12 @@ def main():
     n_gpus = world
     boards, fills, turns = make_roots(args)
     B = args.roots
-    searcher = RootParallelMCTSNC((6, 7), 7, 7, n_trees=args.trees, n_playouts=args.playouts, variant=args.variant,
+    G = GAMES[args.game]
+    A = G["actions"]
+    searcher = RootParallelMCTSNC(G["shape"], G["extra"], A, n_trees=args.trees, n_playouts=args.playouts, variant=args.variant,
                                   search_steps_limit=args.search_steps, max_batch=B, device=local_rank, rank=rank,
-                                  world_size=world, seed=0, ucb_c=2.0, threads_per_tree=args.threads_per_tree)
+                                  world_size=world, seed=0, ucb_c=2.0, threads_per_tree=args.threads_per_tree,
+                                  device_memory=16.0 if args.game == "gomoku" else 2.0)
 
     def barrier():
         if world > 1:
@@ -259,22 +268,22 @@ def main():
     algo_bytes = 32.0 * n_streams + 1300.0 * tree_steps_per_launch
     hbm_achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
     peak_inst = sm_count * 4 * 32 * pk["sm_max_mhz"] * 1e6
-    inst_achieved = plies_per_launch * INST_PER_PLY / (kernel_ms * 1e-3)
+    inst_achieved = plies_per_launch * G["inst_per_ply"] / (kernel_ms * 1e-3)
     line = {
         "metric": "playouts/sec", "value": value, "unit": "playouts/s", "n_gpus": n_gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int32", "data": "synthetic", "config": config_dict(args, n_gpus),
-        "e2e": {"value": e2e_value, "unit": "playouts/s", "h2d_bytes_per_step": int(B * 17),
+        "e2e": {"value": e2e_value, "unit": "playouts/s", "h2d_bytes_per_step": int(B * (17 if args.game == "c4" else 65)),
                 "d2h_bytes_per_step": int(B * (3 * A * 8 + 2 * A + 80)), "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": args.steps * 4,
+        "gpu_launches": args.steps * (4 if args.game == "c4" else 4 + 2 * args.search_steps),
         "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": hbm_achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                     "kernel": "c4::search_kernel<false>", "kernel_ms": kernel_ms,
+                     "kernel": "c4::search_kernel" if args.game == "c4" else "gomoku::playout_kernel (+ tree_step_kernel)", "kernel_ms": kernel_ms,
                      "note": "the search is instruction-issue bound, not HBM bound: see issue_roofline"},
         "issue_roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12,
                            "unit": "T thread-inst/s", "frac": inst_achieved / peak_inst,
                            "plies_per_playout": plies_per_launch / max(playouts_per_launch, 1),
-                           "inst_per_ply_yardstick": INST_PER_PLY, "sm_count": sm_count,
+                           "inst_per_ply_yardstick": G["inst_per_ply"], "sm_count": sm_count,
                            "peak_clock_mhz": pk["sm_max_mhz"]},
         "clocks": clocks, "threads_per_tree": int(thr[0]), "blocks_per_sm": int(per_sm[0]),
         "device_bytes": int(nbytes[0]), "status_bits": status, "ub_draws_per_pass": ub_draws,

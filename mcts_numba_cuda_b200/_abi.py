@@ -23,6 +23,9 @@ E_BAD_ARGUMENT, E_UNSUPPORTED, E_NO_MEMORY, E_BAD_ROOT, E_CAPACITY, E_NO_DEVICE 
 EXPORTED = ["mctsnc_create", "mctsnc_destroy", "mctsnc_reset_rng", "mctsnc_run", "mctsnc_run_batch",
             "mctsnc_search_batch_device", "mctsnc_finish_batch_device", "mctsnc_export", "mctsnc_export_rng",
             "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_error_string"]
+# the PUCT entry points keep the names of the reference's native library (include/puct_b200.h)
+EXPORTED_PUCT = ["puct_select_winner_recalc_launch", "puct_select_virtual_loss_launch", "puct_backup_launch",
+                 "puct_cpp_cuda_error_string"]
 
 
 class Config(ctypes.Structure):

@@ -1,0 +1,344 @@
+// Warp-level PUCT select with virtual loss, plus the backup / release kernels that undo the claims.
+//
+// Drop-in for the reference's only native library, src/puct/puct_gpu_v3_cpp.cu: the exported launcher
+// puct_select_winner_recalc_launch has the same 21 arguments (:450-481) and puct_cpp_cuda_error_string the same
+// meaning (:483-485), so the reference's ctypes binding (src/puct/puct_gpu_v3_cpp.py:84-156) can load this library
+// instead.  Semantics followed (not the code): one warp = one traversal of its tree; per level the progressive-widening
+// quota ceil(c_pw * N^alpha) (:150-157), an expansion ticket by atomicAdd (:219-233), the score
+// W/N + cpuct * P * sqrt(N_parent_eff) / (1 + N + inflight) (:171-180), ties broken by edge id rotated by the warp id
+// (:50-71), the winner claimed with atomicCAS(inflight, seen, seen + 1) and at most two evaluations (:235-275), the
+// path entry (node << 8) | edge (:436), the packed result reason << 25 | kind << 22 | slot << 14 | node (:38-41),
+// and the rollback of every claim of the traversal when it fails (:206-217).
+//
+// What is done differently: a level is ONE pass over the node's edges.  Every lane loads prior / W / N / inflight of
+// its edges once into registers (the four loads of an edge are independent and in flight together), the parent count
+// and the arg-max both come from those registers, and a retry after a lost CAS reloads only `inflight`.  Sums and
+// maxima use the warp-reduce instructions (redux.sync) instead of five rounds of three shuffles, the tie-break is a
+// second redux over the lanes that hold the maximum.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace puct {
+
+constexpr unsigned FULL = 0xFFFFFFFFu;
+constexpr int NODE_TERMINAL = -1;
+constexpr int NODE_LIMIT = 16384, NODE_MASK = 0x3FFF, EDGE_LIMIT = 256;
+constexpr int KIND_SHIFT = 22, SLOT_SHIFT = 14, REASON_SHIFT = 25;
+enum Kind { INVALID = 0, EXPAND = 1, TERMINAL = 2, DEPTH_LIMIT = 3, BUSY = 4 };
+enum Reason {
+    R_UNSET = 0, R_OK_EXPAND = 1, R_OK_TERMINAL = 2, R_OK_DEPTH_LIMIT = 3, R_BUSY_EXPAND_INFLIGHT = 4,
+    R_BUSY_WINNER_RECALC = 5, R_INVALID_SHAPE = 10, R_INVALID_NODE_INFO = 11, R_INVALID_NO_VALID_EDGE = 14,
+    R_INVALID_CHILD_OOB = 15, R_INVALID_UNKNOWN = 16
+};
+constexpr int MAX_EVALUATIONS = 2;
+constexpr float LOWEST = -3.4028234663852886e38f;
+constexpr int NO_EDGE = 0x7FFFFFFF;
+
+__device__ __forceinline__ int pack(int kind, int node, int slot, int reason) {
+    return (reason << REASON_SHIFT) | (kind << KIND_SHIFT) | (slot << SLOT_SHIFT) | node;
+}
+
+__device__ __forceinline__ unsigned ordered(float v) {
+    const unsigned b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// undo the claims of the first `depth` path entries of this warp
+__device__ __forceinline__ void rollback(const int *path, int depth, int lane, int *edge_inflight, long long tree_edges_base,
+                                         int node_cnt, int edges, int amount) {
+    for (int d = lane; d < depth; d += 32) {
+        const int enc = path[d];
+        const int parent = enc >> 8, slot = enc & 0xFF;
+        if (parent >= 0 && parent < node_cnt && slot < edges)
+            atomicSub(&edge_inflight[tree_edges_base + (long long)parent * edges + slot], amount);
+    }
+}
+
+// EPL: edges per lane, ceil(edges / 32) rounded up to 1, 2, 4 or 8 (registers follow it)
+template <int VL_GENERAL, int EPL>
+__global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_winner, const int *__restrict__ edge_child_id,
+                              const float *__restrict__ edge_prior, const float *__restrict__ edge_W,
+                              const int *__restrict__ edge_N, int *edge_inflight, int *node_expand_inflight,
+                              const int *__restrict__ node_expanded, const int *__restrict__ tree_nodes, int *out_selected_node,
+                              int *out_path_eids, int *out_path_len, int trees, int nodes, int edges, int warps,
+                              int path_depth, int virtual_loss) {
+    const int tree = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int wid = threadIdx.x >> 5;
+    const int vl = VL_GENERAL ? virtual_loss : 1;
+    if (tree >= trees || wid >= min((int)(blockDim.x >> 5), warps)) return;
+    const int out_ix = tree * warps + wid;
+    int *path = out_path_eids + (long long)out_ix * path_depth;
+    const int node_cnt = tree_nodes[tree];
+    if (!(path_depth >= 1 && nodes > 0 && node_cnt > 0 && node_cnt <= nodes && node_cnt <= NODE_LIMIT && edges > 0 &&
+          edges <= EDGE_LIMIT)) {
+        if (lane == 0) {
+            out_selected_node[out_ix] = pack(INVALID, NODE_MASK, 0, R_INVALID_SHAPE);
+            out_path_len[out_ix] = 0;
+        }
+        return;
+    }
+    const long long tree_nodes_base = (long long)tree * nodes;
+    const long long tree_edges_base = tree_nodes_base * edges;
+    int result = pack(INVALID, NODE_MASK, 0, R_INVALID_UNKNOWN);
+    int result_len = 0;
+    int node = 0, depth = 0;
+    for (;;) {
+        const int info = node_expanded[tree_nodes_base + node];
+        if (info == NODE_TERMINAL) {
+            result = pack(TERMINAL, node, 0, R_OK_TERMINAL);
+            result_len = depth + 1;
+            break;
+        }
+        if (info < 0 || info > edges) {
+            rollback(path, depth, lane, edge_inflight, tree_edges_base, node_cnt, edges, vl);
+            __syncwarp();
+            result = pack(INVALID, NODE_MASK, 0, R_INVALID_NODE_INFO);
+            break;
+        }
+        if (depth >= path_depth) {
+            result = pack(DEPTH_LIMIT, node, 0, R_OK_DEPTH_LIMIT);
+            result_len = depth + 1;
+            break;
+        }
+        const int n_exp = info;
+        const long long e0 = tree_edges_base + (long long)node * edges;
+        // ---- one pass over the edges: everything the level needs, into registers
+        float prior[EPL], w[EPL];
+        int n[EPL], inflight[EPL];
+        int partial = 0;
+        const bool need_stats = n_exp != 1 || c_pw != 0.0f;
+#pragma unroll
+        for (int k = 0; k < EPL; k++) {
+            const int e = lane + 32 * k;
+            n[k] = 0;
+            inflight[k] = 0;
+            prior[k] = 0.f;
+            w[k] = 0.f;
+            if (need_stats && e < n_exp) {
+                n[k] = edge_N[e0 + e];
+                inflight[k] = edge_inflight[e0 + e];
+                prior[k] = edge_prior[e0 + e];
+                w[k] = edge_W[e0 + e];
+                partial += n[k] + inflight[k];
+            }
+        }
+        int parent_eff = 1, allowed = 1;
+        if (need_stats) {
+            parent_eff = max(__reduce_add_sync(FULL, partial), 1);
+            const float quota = (alpha_pw == 0.5f) ? c_pw * sqrtf((float)parent_eff) : c_pw * powf((float)parent_eff, alpha_pw);
+            allowed = quota >= (float)edges ? edges : max(1, (int)ceilf(quota));
+        }
+        if (allowed > n_exp) {
+            // room for a new child: take a ticket unless the tickets in flight already fill the quota
+            int slot = -1;
+            if (lane == 0) {
+                int *tickets = &node_expand_inflight[tree_nodes_base + node];
+                if (n_exp + *tickets < allowed) {
+                    const int s = n_exp + atomicAdd(tickets, 1);
+                    if (s < allowed) slot = s;
+                    else atomicSub(tickets, 1);
+                }
+            }
+            slot = __shfl_sync(FULL, slot, 0);
+            if (slot >= 0) {
+                result = pack(EXPAND, node, slot, R_OK_EXPAND);
+                result_len = depth + 1;
+                break;
+            }
+            if (n_exp == 0) {
+                rollback(path, depth, lane, edge_inflight, tree_edges_base, node_cnt, edges, vl);
+                __syncwarp();
+                result = pack(BUSY, node, 0, R_BUSY_EXPAND_INFLIGHT);
+                result_len = 0;
+                break;
+            }
+        }
+        // ---- pick an existing child
+        int best = 0, held = 0;
+        if (n_exp == 1) {
+            if (lane == 0) atomicAdd(&edge_inflight[e0], vl);
+            held = 1;
+        } else {
+            const int rot = wid >= n_exp ? wid % n_exp : wid;  // ties go to the edge closest after `rot`
+            const float sqrt_parent = sqrtf((float)parent_eff);
+            for (int attempt = 0;; attempt++) {
+                unsigned my_key = 0;
+                int my_tie = NO_EDGE, my_seen = 0;
+#pragma unroll
+                for (int k = 0; k < EPL; k++) {
+                    const int e = lane + 32 * k;
+                    if (e < n_exp) {
+                        const float q = n[k] > 0 ? w[k] / (float)n[k] : 0.0f;
+                        const float u = cpuct * prior[k] * sqrt_parent / (float)(n[k] + inflight[k] + 1);
+                        const float score = q + u;
+                        if (score >= LOWEST) {  // not NaN, not -inf
+                            const unsigned key = ordered(score);
+                            int tie = e - rot;
+                            if (tie < 0) tie += n_exp;
+                            if (key > my_key || (key == my_key && tie < my_tie)) {
+                                my_key = key;
+                                my_tie = tie;
+                                my_seen = inflight[k];
+                            }
+                        }
+                    }
+                }
+                const unsigned top = __reduce_max_sync(FULL, my_key);
+                const int tie = (int)__reduce_min_sync(FULL, (my_key == top && my_tie != NO_EDGE) ? (unsigned)my_tie : 0xFFFFFFFFu);
+                if (top == 0u || tie < 0) {
+                    best = NO_EDGE;
+                    break;
+                }
+                best = tie + rot;
+                if (best >= n_exp) best -= n_exp;
+                const int owner = __ffs(__ballot_sync(FULL, my_key == top && my_tie == tie)) - 1;
+                const int seen = __shfl_sync(FULL, my_seen, owner);
+                if (lane == 0) held = atomicCAS(&edge_inflight[e0 + best], seen, seen + vl) == seen ? 1 : 0;
+                held = __shfl_sync(FULL, held, 0);
+                if (held || attempt + 1 >= MAX_EVALUATIONS) break;
+                // somebody else moved the winner's count: look at the counts again
+#pragma unroll
+                for (int k = 0; k < EPL; k++) {
+                    const int e = lane + 32 * k;
+                    if (e < n_exp) inflight[k] = *(volatile int *)&edge_inflight[e0 + e];
+                }
+            }
+            if (soft_winner != 0 && !held && best != NO_EDGE) {
+                if (lane == 0) atomicAdd(&edge_inflight[e0 + best], vl);
+                held = 1;
+            }
+        }
+        if (!held) {
+            __syncwarp();
+            rollback(path, depth, lane, edge_inflight, tree_edges_base, node_cnt, edges, vl);
+            __syncwarp();
+            result = best == NO_EDGE ? pack(INVALID, NODE_MASK, 0, R_INVALID_NO_VALID_EDGE) : pack(BUSY, node, 0, R_BUSY_WINNER_RECALC);
+            break;
+        }
+        const int child = edge_child_id[e0 + best];
+        if (child < 0 || child >= node_cnt) {
+            if (lane == 0) atomicSub(&edge_inflight[e0 + best], vl);
+            __syncwarp();
+            rollback(path, depth, lane, edge_inflight, tree_edges_base, node_cnt, edges, vl);
+            __syncwarp();
+            result = pack(INVALID, NODE_MASK, 0, R_INVALID_CHILD_OOB);
+            break;
+        }
+        if (lane == 0) path[depth] = (node << 8) | best;
+        __syncwarp();
+        node = child;
+        depth++;
+    }
+    if (lane == 0) {
+        out_selected_node[out_ix] = result;
+        out_path_len[out_ix] = result_len;
+    }
+}
+
+// Turns the claims of finished traversals into statistics (v3 edge layout; the reference has this step only for its
+// older node-inflight layout, src/puct/puct_gpu_v2.py:847-927): per path edge inflight -= virtual_loss, N += 1,
+// W += value; an EXPAND result also returns its ticket.  With values == NULL only the claims are released
+// (src/puct/test_puct_gpu_v3.py:274-332).
+__global__ void backup_kernel(int virtual_loss, float *edge_W, int *edge_N, int *edge_inflight, int *node_expand_inflight,
+                              const int *__restrict__ tree_nodes, const int *__restrict__ out_selected_node,
+                              const int *__restrict__ out_path_eids, const int *__restrict__ out_path_len,
+                              const float *__restrict__ path_edge_values, int trees, int nodes, int edges, int warps,
+                              int path_depth) {
+    const int tree = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int wid = threadIdx.x >> 5;
+    if (tree >= trees || wid >= min((int)(blockDim.x >> 5), warps)) return;
+    const int node_cnt = tree_nodes[tree];
+    if (node_cnt <= 0 || node_cnt > nodes || node_cnt > NODE_LIMIT) return;
+    const int out_ix = tree * warps + wid;
+    const int raw = out_selected_node[out_ix];
+    if (raw < 0) return;
+    const int kind = (raw >> KIND_SHIFT) & 7;
+    if (kind == INVALID || kind == BUSY) return;
+    const int plen = out_path_len[out_ix];
+    if (plen <= 0) return;
+    const long long tree_edges_base = (long long)tree * nodes * edges;
+    const int *path = out_path_eids + (long long)out_ix * path_depth;
+    for (int d = lane; d < plen - 1; d += 32) {
+        const int enc = path[d];
+        if (enc < 0) continue;
+        const int parent = enc >> 8, slot = enc & 0xFF;
+        if (parent < node_cnt && slot < edges) {
+            const long long ix = tree_edges_base + (long long)parent * edges + slot;
+            atomicSub(&edge_inflight[ix], virtual_loss);
+            if (path_edge_values) {
+                atomicAdd(&edge_N[ix], 1);
+                atomicAdd(&edge_W[ix], path_edge_values[(long long)out_ix * path_depth + d]);
+            }
+        }
+    }
+    if (lane == 0 && kind == EXPAND) {
+        const int leaf = raw & NODE_MASK;
+        if (leaf < node_cnt) atomicSub(&node_expand_inflight[(long long)tree * nodes + leaf], 1);
+    }
+}
+
+template <int VL>
+static int launch_select(float cpuct, float c_pw, float alpha_pw, int soft_winner, int virtual_loss, const int *edge_child_id,
+                         const float *edge_prior, const float *edge_W, const int *edge_N, int *edge_inflight,
+                         int *node_expand_inflight, const int *node_expanded, const int *tree_nodes, int *out_selected_node,
+                         int *out_path_eids, int *out_path_len, int trees, int nodes, int edges, int warps, int path_depth,
+                         cudaStream_t stream) {
+#define PUCT_LAUNCH(E)                                                                                                      \
+    select_kernel<VL, E><<<trees, warps * 32, 0, stream>>>(cpuct, c_pw, alpha_pw, soft_winner, edge_child_id, edge_prior,  \
+                                                          edge_W, edge_N, edge_inflight, node_expand_inflight,             \
+                                                          node_expanded, tree_nodes, out_selected_node, out_path_eids,     \
+                                                          out_path_len, trees, nodes, edges, warps, path_depth, virtual_loss)
+    if (edges <= 32) PUCT_LAUNCH(1);
+    else if (edges <= 64) PUCT_LAUNCH(2);
+    else if (edges <= 128) PUCT_LAUNCH(4);
+    else PUCT_LAUNCH(8);   // more than 256 edges: the kernel itself reports the invalid shape
+#undef PUCT_LAUNCH
+    return (int)cudaGetLastError();
+}
+
+}  // namespace puct
+
+// Same arguments and meaning as puct_select_winner_recalc_launch of src/puct/puct_gpu_v3_cpp.cu:450-481.
+extern "C" int puct_select_winner_recalc_launch(float cpuct, float c_pw, float alpha_pw, int soft_winner, const int *edge_child_id,
+                                                const float *edge_prior, const float *edge_W, const int *edge_N,
+                                                int *edge_inflight, int *node_expand_inflight, const int *node_expanded,
+                                                const int *tree_nodes, int *out_selected_node, int *out_path_eids,
+                                                int *out_path_len, int trees, int nodes, int edges, int warps, int path_depth,
+                                                void *stream) {
+    if (trees <= 0 || warps <= 0 || warps > 32) return (int)cudaErrorInvalidValue;
+    return puct::launch_select<0>(cpuct, c_pw, alpha_pw, soft_winner, 1, edge_child_id, edge_prior, edge_W, edge_N, edge_inflight,
+                                  node_expand_inflight, node_expanded, tree_nodes, out_selected_node, out_path_eids,
+                                  out_path_len, trees, nodes, edges, warps, path_depth, (cudaStream_t)stream);
+}
+
+// The same select with a virtual-loss weight other than 1 (an extension: the reference's select always claims 1).
+extern "C" int puct_select_virtual_loss_launch(float cpuct, float c_pw, float alpha_pw, int soft_winner, int virtual_loss,
+                                               const int *edge_child_id, const float *edge_prior, const float *edge_W,
+                                               const int *edge_N, int *edge_inflight, int *node_expand_inflight,
+                                               const int *node_expanded, const int *tree_nodes, int *out_selected_node,
+                                               int *out_path_eids, int *out_path_len, int trees, int nodes, int edges, int warps,
+                                               int path_depth, void *stream) {
+    if (trees <= 0 || warps <= 0 || warps > 32 || virtual_loss < 1) return (int)cudaErrorInvalidValue;
+    return puct::launch_select<1>(cpuct, c_pw, alpha_pw, soft_winner, virtual_loss, edge_child_id, edge_prior, edge_W, edge_N,
+                                  edge_inflight, node_expand_inflight, node_expanded, tree_nodes, out_selected_node,
+                                  out_path_eids, out_path_len, trees, nodes, edges, warps, path_depth, (cudaStream_t)stream);
+}
+
+// Backup of finished traversals (path_edge_values: float[trees][warps][path_depth], already seen from the side of the
+// player who took the edge) or, with path_edge_values == NULL, release of their claims only.
+extern "C" int puct_backup_launch(int virtual_loss, float *edge_W, int *edge_N, int *edge_inflight, int *node_expand_inflight,
+                                  const int *tree_nodes, const int *out_selected_node, const int *out_path_eids,
+                                  const int *out_path_len, const float *path_edge_values, int trees, int nodes, int edges,
+                                  int warps, int path_depth, void *stream) {
+    if (trees <= 0 || warps <= 0 || warps > 32) return (int)cudaErrorInvalidValue;
+    puct::backup_kernel<<<trees, warps * 32, 0, (cudaStream_t)stream>>>(virtual_loss, edge_W, edge_N, edge_inflight,
+                                                                       node_expand_inflight, tree_nodes, out_selected_node,
+                                                                       out_path_eids, out_path_len, path_edge_values, trees,
+                                                                       nodes, edges, warps, path_depth);
+    return (int)cudaGetLastError();
+}
+
+// Same meaning as puct_cpp_cuda_error_string of src/puct/puct_gpu_v3_cpp.cu:483-485.
+extern "C" const char *puct_cpp_cuda_error_string(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }

@@ -14,19 +14,20 @@ from mcts_numba_cuda_b200.roots import c4_random_roots
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_functions():
-    with open(os.path.join(ROOT, "include", "mctsnc_b200.h")) as f:
+def declared_functions(header, prefix):
+    with open(os.path.join(ROOT, "include", header)) as f:
         text = f.read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mctsnc_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(" + prefix + r"_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
-    names = declared_functions()
-    assert sorted(_abi.EXPORTED) == names
     lib = ctypes.CDLL(_abi.LIB_PATH)
-    for name in names:
-        assert hasattr(lib, name), name
+    for header, prefix, listed in (("mctsnc_b200.h", "mctsnc", _abi.EXPORTED), ("puct_b200.h", "puct", _abi.EXPORTED_PUCT)):
+        names = declared_functions(header, prefix)
+        assert sorted(listed) == names
+        for name in names:
+            assert hasattr(lib, name), name
 
 
 def test_result_struct_layout_matches_numpy_dtype():
