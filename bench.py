@@ -37,6 +37,13 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="search", choices=["search", "puct"],
+                    help="search: the MCTS-NC search (headline); puct: the warp-level PUCT select (BASELINE config 5)")
+    ap.add_argument("--puct-trees", type=int, default=4096)
+    ap.add_argument("--puct-edges", type=int, default=64)
+    ap.add_argument("--puct-depth", type=int, default=16)
+    ap.add_argument("--puct-warps", type=int, default=8)
+    ap.add_argument("--puct-virtual-loss", type=int, default=3)
     ap.add_argument("--game", default="c4", choices=sorted(GAMES))
     ap.add_argument("--roots", type=int, default=256)
     ap.add_argument("--search-steps", type=int, default=2000)
@@ -173,8 +180,109 @@ def run_reference(args, rank):
                       "gpu_launches": 0}))
 
 
+def puct_device_case(trees, edges, depth, warps, seed, device):
+    """The layered workload of oracle.puct_oracle.layered_case, generated on the device (4096 x 1025 x 64 edges would
+    take minutes and gigabytes on the host): level l+1 holds `edges` nodes shared by the nodes of level l, the last level
+    is terminal; priors ~ Dirichlet(0.3), visit counts ~ U{0..49}, W = N * U[-1, 1]."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    per = edges
+    nodes = 1 + per * depth
+    level_of = torch.zeros(nodes, dtype=torch.long, device=device)
+    level_of[1:] = (torch.arange(nodes - 1, device=device) // per) + 1
+    idx_in_level = torch.zeros(nodes, dtype=torch.long, device=device)
+    idx_in_level[1:] = torch.arange(nodes - 1, device=device) % per
+    nxt = 1 + per * level_of[:, None] + (torch.arange(edges, device=device)[None, :] + idx_in_level[:, None]) % per
+    expanded = torch.full((nodes,), edges, dtype=torch.int32, device=device)
+    expanded[level_of == depth] = -1
+    nxt[level_of == depth] = -1
+    gamma = torch._standard_gamma(torch.full((trees, nodes, edges), 0.3, device=device), generator=g)
+    prior = (gamma / gamma.sum(dim=2, keepdim=True).clamp_min(1e-30)).float()
+    n = torch.randint(0, 50, (trees, nodes, edges), device=device, generator=g, dtype=torch.int32)
+    w = n.float() * (torch.rand((trees, nodes, edges), device=device, generator=g) * 2 - 1)
+    return {"edge_child": nxt.to(torch.int32)[None].expand(trees, -1, -1).contiguous(), "edge_prior": prior.contiguous(),
+            "edge_w": w.contiguous(), "edge_n": n.contiguous(),
+            "edge_inflight": torch.zeros((trees, nodes, edges), dtype=torch.int32, device=device),
+            "node_expand_inflight": torch.zeros((trees, nodes), dtype=torch.int32, device=device),
+            "node_expanded": expanded[None].expand(trees, -1).contiguous(),
+            "node_count": torch.full((trees,), nodes, dtype=torch.int32, device=device),
+            "out_selected": torch.zeros((trees, warps), dtype=torch.int32, device=device),
+            "out_path": torch.full((trees, warps, depth), -1, dtype=torch.int32, device=device),
+            "out_len": torch.zeros((trees, warps), dtype=torch.int32, device=device), "trees": trees, "warps": warps}
+
+
+def run_puct(args):
+    """Select-only timing as the reference's own benchmark does it (src/puct/test_puct_gpu_v3.py:632-650): CUDA events
+    around the select launch, an untimed release after each; sel/s = trees * warps / mean select time."""
+    import ctypes
+    import torch
+    from mcts_numba_cuda_b200 import _abi, puct
+    _abi.lib()
+    dev = "cuda:0"
+    T, E, D, Wp, vl = args.puct_trees, args.puct_edges, args.puct_depth, args.puct_warps, args.puct_virtual_loss
+    d = puct_device_case(T, E, D, Wp, 0, dev)
+    pk = peaks()
+
+    def timed(select):
+        times = []
+        for i in range(args.warmup + args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            select()
+            e1.record()
+            torch.cuda.synchronize()
+            valid = int((((d["out_selected"] >> 22) & 7) != 4).sum())
+            puct.launch_release(d, virtual_loss=release_vl[0])
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        assert int(d["edge_inflight"].abs().sum()) == 0
+        return float(np.mean(times)), valid
+
+    release_vl = [vl]
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms, valid = timed(lambda: puct.launch_select(d, cpuct=1.5, c_pw=0.0, virtual_loss=vl))
+    release_vl[0] = 1
+    ms_vl1, valid1 = timed(lambda: puct.launch_select(d, cpuct=1.5, c_pw=0.0, virtual_loss=1))
+    ref_ms = None
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libpuct_ref_sm100a.so")
+    if os.path.exists(ref_path):
+        lib = ctypes.CDLL(ref_path)
+        vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        lib.puct_select_winner_recalc_launch.argtypes = [f32, f32, f32, i32] + [vp] * 11 + [i32] * 5 + [vp]
+        ptrs = [ctypes.c_void_p(d[k].data_ptr()) for k in ("edge_child", "edge_prior", "edge_w", "edge_n", "edge_inflight",
+                                                            "node_expand_inflight", "node_expanded", "node_count",
+                                                            "out_selected", "out_path", "out_len")]
+        nodes = d["edge_child"].shape[1]
+        ref_ms, _ = timed(lambda: lib.puct_select_winner_recalc_launch(1.5, 0.0, 0.5, 0, *ptrs, T, nodes, E, Wp, D,
+                                                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    clocks = sampler.stop()
+    sel = T * Wp
+    bytes_per_sel = D * (16 * E + 16)          # prior, W, N, inflight per edge + node record, child id, path entry, ticket
+    achieved = sel * bytes_per_sel / (ms * 1e-3) / 1e9
+    line = {"metric": "PUCT selections/sec (select kernel only, CUDA events)", "value": sel / (ms * 1e-3), "unit": "selections/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"PUCT warp-level select: {T} trees x {E} edges, layered depth {D}, {Wp} warps per tree, "
+                                   f"virtual loss {vl}, c_puct 1.5, priors ~ Dirichlet(0.3)",
+                       "l2": f"edge arrays {5 * 4 * T * (1 + E * D) * E / 1e9:.1f} GB exceed the 126 MB L2"},
+            "valid_selections": valid, "virtual_loss_1": {"value": sel / (ms_vl1 * 1e-3), "ms": ms_vl1, "valid": valid1},
+            "reference_kernel": None if ref_ms is None else {"value": sel / (ref_ms * 1e-3), "ms": ref_ms,
+                                                             "what": "src/puct/puct_gpu_v3_cpp.cu built for sm_100a, virtual loss 1"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                         "kernel": "puct::select_kernel", "bytes_per_selection": bytes_per_sel},
+            "gpu_launches": 2 * (args.steps + args.warmup) * 2, "clocks": clocks}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
+    if args.workload == "puct":
+        run_puct(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

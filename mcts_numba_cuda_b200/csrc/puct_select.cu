@@ -10,10 +10,12 @@
 // path entry (node << 8) | edge (:436), the packed result reason << 25 | kind << 22 | slot << 14 | node (:38-41),
 // and the rollback of every claim of the traversal when it fails (:206-217).
 //
-// What is done differently: a level is ONE pass over the node's edges.  Every lane loads prior / W / N / inflight of
-// its edges once into registers (the four loads of an edge are independent and in flight together), the parent count
-// and the arg-max both come from those registers, and a retry after a lost CAS reloads only `inflight`.  Sums and
-// maxima use the warp-reduce instructions (redux.sync) instead of five rounds of three shuffles, the tie-break is a
+// What is done differently: the traversal is latency-bound (dependent loads from gigabytes of edge arrays), so a level
+// is built to cost ONE memory round trip instead of four.  Every lane keeps child / prior / W / N / inflight of its
+// edges in registers; the parent count and the arg-max both come from those registers; and as soon as the winner is
+// known, the claim (atomicCAS), the child's node record and ALL the child's edges are requested together, so that the
+// next level starts with its data already on the way.  A retry after a lost CAS reloads only `inflight`.  Sums and
+// maxima use the warp-reduce instructions (redux.sync) instead of five rounds of three shuffles; the tie-break is a
 // second redux over the lanes that hold the maximum.
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -54,6 +56,37 @@ __device__ __forceinline__ void rollback(const int *path, int depth, int lane, i
     }
 }
 
+// the edges of one node as seen by one lane (edge lane + 32 k in slot k)
+template <int EPL>
+struct EdgeRegs {
+    float prior[EPL], w[EPL];
+    int n[EPL], inflight[EPL], child[EPL];
+};
+
+// requests all `edges` slots of a node, expanded or not (the arrays are dense, so the addresses are valid): used
+// before the node's record has arrived, i.e. before the number of expanded edges is known
+template <int EPL>
+__device__ __forceinline__ void load_edges(EdgeRegs<EPL> &r, long long e0, int lane, int edges, const int *edge_child_id,
+                                           const float *edge_prior, const float *edge_W, const int *edge_N,
+                                           const int *edge_inflight) {
+#pragma unroll
+    for (int k = 0; k < EPL; k++) {
+        const int e = lane + 32 * k;
+        r.n[k] = 0;
+        r.inflight[k] = 0;
+        r.prior[k] = 0.f;
+        r.w[k] = 0.f;
+        r.child[k] = -1;
+        if (e < edges) {
+            r.child[k] = edge_child_id[e0 + e];
+            r.n[k] = edge_N[e0 + e];
+            r.inflight[k] = *(volatile const int *)&edge_inflight[e0 + e];
+            r.prior[k] = edge_prior[e0 + e];
+            r.w[k] = edge_W[e0 + e];
+        }
+    }
+}
+
 // EPL: edges per lane, ceil(edges / 32) rounded up to 1, 2, 4 or 8 (registers follow it)
 template <int VL_GENERAL, int EPL>
 __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_winner, const int *__restrict__ edge_child_id,
@@ -83,8 +116,11 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
     int result = pack(INVALID, NODE_MASK, 0, R_INVALID_UNKNOWN);
     int result_len = 0;
     int node = 0, depth = 0;
+    int info = node_expanded[tree_nodes_base];
+    EdgeRegs<EPL> cur, nxt;
+    load_edges<EPL>(cur, tree_edges_base, lane, edges, edge_child_id, edge_prior, edge_W, edge_N, edge_inflight);
+    nxt = cur;
     for (;;) {
-        const int info = node_expanded[tree_nodes_base + node];
         if (info == NODE_TERMINAL) {
             result = pack(TERMINAL, node, 0, R_OK_TERMINAL);
             result_len = depth + 1;
@@ -103,26 +139,12 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
         }
         const int n_exp = info;
         const long long e0 = tree_edges_base + (long long)node * edges;
-        // ---- one pass over the edges: everything the level needs, into registers
-        float prior[EPL], w[EPL];
-        int n[EPL], inflight[EPL];
+        // ---- the edges of this node are in registers already (requested while the level above was being decided)
         int partial = 0;
         const bool need_stats = n_exp != 1 || c_pw != 0.0f;
 #pragma unroll
-        for (int k = 0; k < EPL; k++) {
-            const int e = lane + 32 * k;
-            n[k] = 0;
-            inflight[k] = 0;
-            prior[k] = 0.f;
-            w[k] = 0.f;
-            if (need_stats && e < n_exp) {
-                n[k] = edge_N[e0 + e];
-                inflight[k] = edge_inflight[e0 + e];
-                prior[k] = edge_prior[e0 + e];
-                w[k] = edge_W[e0 + e];
-                partial += n[k] + inflight[k];
-            }
-        }
+        for (int k = 0; k < EPL; k++)
+            if (lane + 32 * k < n_exp) partial += cur.n[k] + cur.inflight[k];
         int parent_eff = 1, allowed = 1;
         if (need_stats) {
             parent_eff = max(__reduce_add_sync(FULL, partial), 1);
@@ -155,8 +177,16 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
             }
         }
         // ---- pick an existing child
-        int best = 0, held = 0;
+        // The child of every edge is in a register already, so as soon as the winner is known its node record can be
+        // requested together with the claim instead of after it: one memory round trip per level less.
+        int best = 0, held = 0, child = -1, next_info = 0;
         if (n_exp == 1) {
+            child = __shfl_sync(FULL, cur.child[0], 0);
+            if (child >= 0 && child < node_cnt) {
+                next_info = node_expanded[tree_nodes_base + child];
+                load_edges<EPL>(nxt, tree_edges_base + (long long)child * edges, lane, edges, edge_child_id, edge_prior, edge_W,
+                                edge_N, edge_inflight);
+            }
             if (lane == 0) atomicAdd(&edge_inflight[e0], vl);
             held = 1;
         } else {
@@ -164,13 +194,13 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
             const float sqrt_parent = sqrtf((float)parent_eff);
             for (int attempt = 0;; attempt++) {
                 unsigned my_key = 0;
-                int my_tie = NO_EDGE, my_seen = 0;
+                int my_tie = NO_EDGE, my_seen = 0, my_child = -1;
 #pragma unroll
                 for (int k = 0; k < EPL; k++) {
                     const int e = lane + 32 * k;
                     if (e < n_exp) {
-                        const float q = n[k] > 0 ? w[k] / (float)n[k] : 0.0f;
-                        const float u = cpuct * prior[k] * sqrt_parent / (float)(n[k] + inflight[k] + 1);
+                        const float q = cur.n[k] > 0 ? cur.w[k] / (float)cur.n[k] : 0.0f;
+                        const float u = cpuct * cur.prior[k] * sqrt_parent / (float)(cur.n[k] + cur.inflight[k] + 1);
                         const float score = q + u;
                         if (score >= LOWEST) {  // not NaN, not -inf
                             const unsigned key = ordered(score);
@@ -179,7 +209,8 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
                             if (key > my_key || (key == my_key && tie < my_tie)) {
                                 my_key = key;
                                 my_tie = tie;
-                                my_seen = inflight[k];
+                                my_seen = cur.inflight[k];
+                                my_child = cur.child[k];
                             }
                         }
                     }
@@ -194,6 +225,12 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
                 if (best >= n_exp) best -= n_exp;
                 const int owner = __ffs(__ballot_sync(FULL, my_key == top && my_tie == tie)) - 1;
                 const int seen = __shfl_sync(FULL, my_seen, owner);
+                child = __shfl_sync(FULL, my_child, owner);
+                if (child >= 0 && child < node_cnt) {  // the next level's data travels together with the claim
+                    next_info = node_expanded[tree_nodes_base + child];
+                    load_edges<EPL>(nxt, tree_edges_base + (long long)child * edges, lane, edges, edge_child_id, edge_prior,
+                                    edge_W, edge_N, edge_inflight);
+                }
                 if (lane == 0) held = atomicCAS(&edge_inflight[e0 + best], seen, seen + vl) == seen ? 1 : 0;
                 held = __shfl_sync(FULL, held, 0);
                 if (held || attempt + 1 >= MAX_EVALUATIONS) break;
@@ -201,7 +238,7 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
 #pragma unroll
                 for (int k = 0; k < EPL; k++) {
                     const int e = lane + 32 * k;
-                    if (e < n_exp) inflight[k] = *(volatile int *)&edge_inflight[e0 + e];
+                    if (e < n_exp) cur.inflight[k] = *(volatile int *)&edge_inflight[e0 + e];
                 }
             }
             if (soft_winner != 0 && !held && best != NO_EDGE) {
@@ -216,7 +253,6 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
             result = best == NO_EDGE ? pack(INVALID, NODE_MASK, 0, R_INVALID_NO_VALID_EDGE) : pack(BUSY, node, 0, R_BUSY_WINNER_RECALC);
             break;
         }
-        const int child = edge_child_id[e0 + best];
         if (child < 0 || child >= node_cnt) {
             if (lane == 0) atomicSub(&edge_inflight[e0 + best], vl);
             __syncwarp();
@@ -228,6 +264,8 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
         if (lane == 0) path[depth] = (node << 8) | best;
         __syncwarp();
         node = child;
+        info = next_info;
+        cur = nxt;
         depth++;
     }
     if (lane == 0) {
