@@ -474,21 +474,26 @@ const void *search_kernel_ptr(const mctsnc_config &c) {
     return is_ocp(c) ? (const void *)c4::search_kernel<true> : (const void *)c4::search_kernel<false>;
 }
 
-// threads of the block that grows one tree: the largest of 256/128/64 for which `trees` blocks are resident at once,
-// so that a batch runs as one wave; 256 when even 64 does not fit
+// threads of the block that grows one tree.  Many trees (throughput regime, at least two per SM): 384, the best
+// of a measured sweep 96..512 on the headline workload (the kernel is bound by the integer pipe, block size matters
+// by less than 10 %).  Few trees: the largest of 256 / 128 / 64 for which all blocks are resident at once.
 int choose_threads(mctsnc_handle *h, long long trees) {
+    const void *fn = search_kernel_ptr(h->cfg);
+    int per_sm = 0;
+    if (trees >= 2LL * h->sm_count) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 384, h->dyn_smem);
+        h->blocks_per_sm = per_sm;
+        return 384;
+    }
     const int candidates[3] = {256, 128, 64};
     for (int i = 0; i < 3; i++) {
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, search_kernel_ptr(h->cfg), candidates[i], h->dyn_smem) != cudaSuccess)
-            continue;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, candidates[i], h->dyn_smem) != cudaSuccess) continue;
         if ((long long)per_sm * h->sm_count >= trees) {
             h->blocks_per_sm = per_sm;
             return candidates[i];
         }
     }
-    int per_sm = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, search_kernel_ptr(h->cfg), 256, h->dyn_smem);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 256, h->dyn_smem);
     h->blocks_per_sm = per_sm;
     return 256;
 }
