@@ -85,6 +85,7 @@ struct mctsnc_handle {
     int *path_ns = nullptr, *path_wins = nullptr;
     signed char *child_outcome = nullptr;
     unsigned char *child_action = nullptr;
+    unsigned char *active_rank = nullptr;
     unsigned *root_gboard = nullptr;      // [max_batch][16]
     unsigned *h_root_gboard = nullptr;
     long long *sums = nullptr;            // [max_batch][3A]
@@ -456,6 +457,7 @@ void release(mctsnc_handle *h) {
     cudaFree(h->path_wins);
     cudaFree(h->child_outcome);
     cudaFree(h->child_action);
+    cudaFree(h->active_rank);
     cudaFree(h->root_gboard);
     cudaFreeHost(h->h_root_gboard);
     cudaFree(h->sums);
@@ -548,6 +550,7 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
     p.child_out = h->child_out;
     p.child_outcome = h->child_outcome;
     p.child_action = h->child_action;
+    p.active_rank = h->active_rank;
     p.rng_playout = h->rng_playout;
     p.rng_expand = h->rng_expand;
     p.root_board = h->root_gboard;
@@ -561,16 +564,22 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
     const unsigned trees = (unsigned)((long long)batch * h->cfg.n_trees);
     const bool ocp = is_ocp(h->cfg);
     const int P = h->cfg.n_playouts;
-    const dim3 pgrid(gomoku::A, trees);
-    h->threads = 256;
+    // persistent playout grid: as many blocks as fit on the device at once (three per SM, limited by shared memory)
+    int per_sm = 0;
+    const void *pk = ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pk, gomoku::DYN_THREADS, h->dyn_smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const unsigned pgrid = (unsigned)(per_sm * h->sm_count);
+    h->threads = gomoku::DYN_THREADS;
+    h->blocks_per_sm = per_sm;
+    (void)P;
     for (int s = 0; s <= steps; s++) {
         p.first = (first && s == 0) ? 1 : 0;
         p.backup_only = s == steps ? 1 : 0;
         if (ocp) gomoku::tree_step_kernel<true><<<trees, 256, 0, stream>>>(p);
         else gomoku::tree_step_kernel<false><<<trees, 256, 0, stream>>>(p);
         if (s == steps) break;
-        if (ocp) gomoku::playout_kernel<true><<<pgrid, P, h->dyn_smem, stream>>>(p);
-        else gomoku::playout_kernel<false><<<pgrid, P, h->dyn_smem, stream>>>(p);
+        if (ocp) gomoku::playout_dynamic_kernel<true><<<pgrid, gomoku::DYN_THREADS, h->dyn_smem, stream>>>(p, (int)trees);
+        else gomoku::playout_dynamic_kernel<false><<<pgrid, gomoku::DYN_THREADS, h->dyn_smem, stream>>>(p, (int)trees);
     }
     return (int)cudaGetLastError();
 }
@@ -681,8 +690,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
         if (c.board_rows != c4::ROWS || c.board_cols != c4::COLS || c.max_actions != c4::A || c.extra_info_memory != c4::COLS)
             return MCTSNC_E_UNSUPPORTED;
     } else if (c.game == MCTSNC_GAME_GOMOKU) {
-        if (c.board_rows != gomoku::M || c.board_cols != gomoku::N || c.max_actions != gomoku::A || c.extra_info_memory > 1 ||
-            c.n_playouts < 32)
+        if (c.board_rows != gomoku::M || c.board_cols != gomoku::N || c.max_actions != gomoku::A || c.extra_info_memory > 1)
             return MCTSNC_E_UNSUPPORTED;
     } else {
         return MCTSNC_E_UNSUPPORTED;
@@ -717,9 +725,9 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     const bool ocp = is_ocp(c);
     h->rng_per_search = ocp ? (long long)c.n_trees * c.n_playouts : (long long)c.n_trees * h->A * c.n_playouts;
     h->dyn_smem = sizeof(ulonglong2) * (size_t)(h->rng_per_search / c.n_trees);
-    if (is_gomoku(c)) h->dyn_smem = sizeof(unsigned) * (size_t)gomoku::THREAD_WORDS * c.n_playouts;   // per-thread game state
+    if (is_gomoku(c)) h->dyn_smem = sizeof(unsigned) * (size_t)gomoku::THREAD_WORDS * (gomoku::DYN_THREADS + gomoku::DYN_THREADS / 32);   // per-thread game state + per-warp templates
     if (h->dyn_smem > 48 * 1024) {
-        const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_kernel<true> : (const void *)gomoku::playout_kernel<false>)
+        const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>)
                                           : search_kernel_ptr(c);
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
         if (e != cudaSuccess) {
@@ -736,6 +744,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->path_wins, h->n_trees_total * PATH_CAP);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->child_outcome, h->n_trees_total * h->A);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->child_action, h->n_trees_total * h->A);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->active_rank, h->n_trees_total * h->A);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->root_gboard, (long long)c.max_batch * 16);
     if (!rc && is_gomoku(c) && cudaMallocHost((void **)&h->h_root_gboard, sizeof(unsigned) * 16 * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && is_gomoku(c)) rc = (int)cudaMemset(h->gstep, 0, sizeof(gomoku::StepInfo) * h->n_trees_total);
