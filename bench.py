@@ -30,6 +30,10 @@ GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0,
          "gomoku": {"shape": (15, 15), "extra": 0, "actions": 225, "inst_per_ply": 100.0, "name": "Gomoku 15x15"}}
 # inst_per_ply: thread instructions of one playout ply (yardstick of the issue roofline)
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one search-kernel launch, from a one-pass ncu capture of the default
+# workload (profiles/c4_acp_search_kernel_full_size_traffic.md); key: game, variant, trees, playouts, search steps, roots
+MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 55367168 + 341450496}
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -53,7 +57,7 @@ def parse_args():
     ap.add_argument("--max-plies", type=int, default=20)
     ap.add_argument("--threads-per-tree", type=int, default=0)
     ap.add_argument("--cpu-sample-roots", type=int, default=0, help="roots of the CPU baseline sample (0 = choose)")
-    ap.add_argument("--cpu-sample-steps", type=int, default=150)
+    ap.add_argument("--cpu-sample-steps", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -385,7 +389,10 @@ def main():
                 "d2h_bytes_per_step": int(B * (3 * A * 8 + 2 * A + 80)), "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": args.steps * (4 if args.game == "c4" else 4 + 2 * args.search_steps),
         "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": hbm_achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "frac": hbm_achieved / pk["hbm_gbs"],
+                     "traffic": MEASURED_TRAFFIC_BYTES.get((args.game, args.variant, args.trees, args.playouts, args.search_steps, B)),
+                     "traffic_unit": "bytes per launch (ncu, one capture)", "algorithmic_bytes": algo_bytes,
+                     "peak_source": pk["source"],
                      "kernel": "c4::search_kernel" if args.game == "c4" else "gomoku::playout_kernel (+ tree_step_kernel)", "kernel_ms": kernel_ms,
                      "note": "the search is instruction-issue bound, not HBM bound: see issue_roofline"},
         "issue_roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12,
@@ -399,7 +406,7 @@ def main():
     }
     if n_gpus == 1 and not args.no_cpu_baseline:
         steps = args.cpu_sample_steps
-        n_roots = args.cpu_sample_roots or 4
+        n_roots = args.cpu_sample_roots or 8
         playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, 1, n_roots, steps)
         line["cpu_baseline"] = {"value": playouts / wall, "unit": "playouts/s", "cores": 1, "kind": "port",
                                 "sample": f"{n_roots} roots x {steps} search steps, sequential, {wall:.1f} s"}
