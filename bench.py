@@ -28,10 +28,12 @@ if ROOT not in sys.path:
 
 GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0, "name": "Connect-4 6x7"},
          "gomoku": {"shape": (15, 15), "extra": 0, "actions": 225, "inst_per_ply": 100.0, "name": "Gomoku 15x15"}}
-# inst_per_ply: thread instructions of one playout ply (yardstick of the issue roofline)
+# inst_per_ply: thread instructions of one playout ply in a bitboard / row-mask formulation: RNG step ~20, draw -> ordinal 5,
+# move pick and placement ~18, line test through the new stone 16 (Connect 4) / ~55 (Gomoku), draw test and loop ~6.
+# It is the yardstick of the issue roofline, not a count of the compiled code.
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one search-kernel launch, from a one-pass ncu capture of the default
-# workload (profiles/c4_acp_search_kernel_full_size_traffic.md); key: game, variant, trees, playouts, search steps, roots
+# workload; key: game, variant, trees, playouts, search steps, roots
 MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 55367168 + 341450496}
 
 
@@ -374,7 +376,7 @@ def main():
     plies_per_launch = plies_per_pass / n_gpus
     playouts_per_launch = playouts_per_pass / n_gpus
     tree_steps_per_launch = B * args.trees * args.search_steps
-    # algorithmic HBM bytes (DESIGN.md): every stream state is read and written once per launch (2 x 16 B), and a
+    # algorithmic HBM bytes: every stream state is read and written once per launch (2 x 16 B), and a
     # tree-step touches ~1.3 KB of tree records
     n_streams = B * args.trees * (A if "acp" in args.variant else 1) * args.playouts
     algo_bytes = 32.0 * n_streams + 1300.0 * tree_steps_per_launch

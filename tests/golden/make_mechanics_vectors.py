@@ -62,4 +62,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <root of the reference checkout>")
+    main(sys.argv[1])
