@@ -292,11 +292,16 @@ __global__ void search_kernel(const SearchParams p) {
                 s.path_ns[0] = r.x;
                 s.path_wins[0] = r.y;
             }
+            // log(N) of the node being left is needed by every child's UCB; each lane computes the logarithm of ITS child's
+            // count while it evaluates the child's UCB (two independent float64 chains), so the winner's value is ready
+            // for the next level instead of starting that level with a ~100-operation dependent chain
+            double log_parent = (r.w & 0x7F) != 0 ? log((double)r.x) : 0.0;
             while ((r.w & 0x7F) != 0 && depth < 46) {
                 const unsigned mask = r.w & 0x7F;
                 int child = -1;
                 int4 cr = make_int4(0, 0, -1, 0);
                 unsigned key = 0;
+                double log_child = 0.0;
                 if (lane < A && ((mask >> lane) & 1u)) {
                     child = r.z + __popc(mask & ((1u << lane) - 1u));
                     cr = rec[child];
@@ -307,8 +312,9 @@ __global__ void search_kernel(const SearchParams p) {
                         // src/mctsnc.py:1337 -- evaluated in float64 (numba promotes int32/float32 and log(int32) to
                         // float64), fused multiply-add as NVVM contracts it, rounded once to float32
                         const double q = (double)cr.y / (double)__int2float_rn(cr.x);
-                        const double e = sqrt(log((double)r.x) / (double)cr.x);
+                        const double e = sqrt(log_parent / (double)cr.x);
                         v = __double2float_rn(fma(c_ucb, e, q));
+                        log_child = log((double)cr.x);
                     }
                     key = ordered_key(v);
                 }
@@ -320,6 +326,7 @@ __global__ void search_kernel(const SearchParams p) {
                 r.y = __shfl_sync(0xFFFFFFFFu, cr.y, w);
                 r.z = __shfl_sync(0xFFFFFFFFu, cr.z, w);
                 r.w = __shfl_sync(0xFFFFFFFFu, cr.w, w);
+                log_parent = __shfl_sync(0xFFFFFFFFu, log_child, w);
                 depth++;
                 if (lane == 0) {
                     s.path[depth] = node;

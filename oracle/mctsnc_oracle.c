@@ -785,6 +785,9 @@ int mo_run(mo_ctx *c, const int8_t *root_board, const int8_t *root_extra, int ro
     if (!root_extra) { root_extra = &zero; root_extra_len = 1; }
     k_reset(c, root_board, root_extra, root_extra_len, root_turn);
     c->steps = 0;
+    c->plies = 0;      /* the bookkeeping counters describe one search */
+    c->ub_draws = 0;
+    c->tree_full_events = 0;
     for (int64_t step = 0; step < steps; step++) {
         for (int ti = 0; ti < T; ti++) {
             if ((int64_t)c->trees_sizes[ti] + A > c->cap && c->cap < c->max_tree_size) { c->error |= 8; return c->error; }

@@ -146,3 +146,15 @@ def test_final_argmax_tie_rule():
     assert reduce_over_actions_host(flags, n, w, expanded, thrifty=True)[0] == 1       # ordinals 0,1,3,5 tie -> ordinal 0
     flags[3] = True
     assert reduce_over_actions_host(flags, n, w, np.ones(7, bool), thrifty=False) == (3, True, 1, 0)
+
+
+def test_drop_in_import_as_top_level_module():
+    """The reference's callers do `from mctsnc import MCTSNC` (src/game_runner.py:2, src/main.py:27): with the package
+    directory on sys.path that import gives this implementation."""
+    import subprocess
+    import sys
+    pkg = os.path.join(ROOT, "mcts_numba_cuda_b200")
+    code = ("import sys; sys.path.insert(0, %r); from mctsnc import MCTSNC; "
+            "ai = MCTSNC((6, 7), 7, 7, verbose_info=False); print(type(ai).__module__, ai.variant)" % pkg)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True).stdout.split()
+    assert out == ["mctsnc", "acp_prodigal"]

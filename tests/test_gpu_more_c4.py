@@ -178,3 +178,41 @@ def test_ub_draws_are_replayed_like_the_oracle():
     assert orc.ub_draws > 0 and ai._res["ub_draws"] == orc.ub_draws
     assert ai._res["status"] & _abi.STATUS_UB_DRAW
     compare_trees(ai, orc)
+
+
+@pytest.mark.parametrize("variant,n_trees,n_playouts,steps,ucb_c,seed", [
+    ("acp_prodigal", 2, 512, 60, 2.0, 0),      # largest n_playouts: 56 KB of stream states per block (opt-in shared memory)
+    ("ocp_prodigal", 3, 512, 150, 0.5, 7),
+    ("acp_thrifty", 2, 1, 200, 2.0, 1),        # smallest n_playouts
+    ("ocp_thrifty", 5, 2, 300, 1.0, 2),
+    ("acp_prodigal", 64, 32, 25, 3.5, 123456789),   # many trees, another seed and exploration constant
+    ("ocp_thrifty", 1, 32, 200, 2.0, 0),       # BASELINE config 1 shape
+])
+def test_edge_sizes_match_oracle(variant, n_trees, n_playouts, steps, ucb_c, seed):
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=n_trees, n_playouts=n_playouts,
+                variant=variant, ucb_c=ucb_c, seed=seed, verbose_info=False)
+    ai.init_device_side_arrays()
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=n_trees, n_playouts=n_playouts, variant=variant, ucb_c=ucb_c, seed=seed,
+                       node_capacity=steps * 7 + 8)
+    boards, fills, turns = c4_random_roots(2, 12, seed=seed % 1000)
+    for b in range(2):
+        best = ai.run(boards[b], fills[b], int(turns[b]))
+        orc.run(boards[b], fills[b], int(turns[b]), steps)
+        compare_trees(ai, orc)
+        assert int(best) == orc.best_action
+        assert ai._res["plies"] == orc.plies
+
+
+def test_tree_full_is_reported_not_followed():
+    """A tiny memory budget (max_tree_size = 40 by the reference's formula, src/mctsnc.py:350-358): the trees stop growing,
+    the status says so, nothing is written out of bounds."""
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=100, n_trees=2, n_playouts=32,
+                variant="acp_prodigal", verbose_info=False, device_memory=24200 / 2 ** 30)
+    ai.init_device_side_arrays()
+    assert ai.max_tree_size == 40
+    ai.run(np.zeros((6, 7), np.int8), np.zeros(7, np.int8), 1)
+    assert ai.status & _abi.STATUS_TREE_FULL
+    sizes = ai.export("trees_sizes")
+    assert (sizes <= 40).all() and (sizes > 30).all()
+    ns = ai.export("trees_ns", max_nodes=40)
+    assert (ns[:, 0] > 0).all() and ai.steps == 100
