@@ -34,7 +34,7 @@ GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0,
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one search-kernel launch, from a one-pass ncu capture of the default
 # workload; key: game, variant, trees, playouts, search steps, roots
-MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 55367168 + 341450496}
+MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 126915584 + 405630208}
 
 
 def parse_args():
@@ -378,8 +378,12 @@ def main():
     tree_steps_per_launch = B * args.trees * args.search_steps
     # algorithmic HBM bytes: every stream state is read and written once per launch (2 x 16 B), and a
     # tree-step touches ~1.3 KB of tree records
+    # A Connect-4 batch with more trees than resident blocks runs in slices of 32 steps taken from a work queue; a
+    # tree's streams are then read and written once per slice (they fit in L2 between slices for the headline batch).
+    queued = args.game == "c4" and B * args.trees > int(per_sm[0]) * sm_count and args.search_steps > 32
+    slices = -(-args.search_steps // 32) if queued else 1
     n_streams = B * args.trees * (A if "acp" in args.variant else 1) * args.playouts
-    algo_bytes = 32.0 * n_streams + 1300.0 * tree_steps_per_launch
+    algo_bytes = 32.0 * n_streams * slices + 1300.0 * tree_steps_per_launch
     hbm_achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
     peak_inst = sm_count * 4 * 32 * pk["sm_max_mhz"] * 1e6
     inst_achieved = plies_per_launch * G["inst_per_ply"] / (kernel_ms * 1e-3)
@@ -389,7 +393,7 @@ def main():
         "vs_baseline": None, "dtype": "int32", "data": "synthetic", "config": config_dict(args, n_gpus),
         "e2e": {"value": e2e_value, "unit": "playouts/s", "h2d_bytes_per_step": int(B * (17 if args.game == "c4" else 65)),
                 "d2h_bytes_per_step": int(B * (3 * A * 8 + 2 * A + 80)), "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": args.steps * (4 if args.game == "c4" else 4 + 2 * args.search_steps),
+        "gpu_launches": args.steps * ((6 if queued else 4) if args.game == "c4" else 4 + 2 * args.search_steps),
         "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": hbm_achieved / pk["hbm_gbs"],
                      "traffic": MEASURED_TRAFFIC_BYTES.get((args.game, args.variant, args.trees, args.playouts, args.search_steps, B)),

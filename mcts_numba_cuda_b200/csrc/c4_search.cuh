@@ -194,6 +194,7 @@ struct Shared {
     // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the bit position of the
     // column's bottom cell (7 * column) in the low byte and the column's bit (1 << column) in the high byte
     unsigned short move_lut[128 * 8];
+    int job;                 // tree of the slice being run (-1: none left)
     int n_slots;
     int next_item;           // next game to hand out in the playout phase
     int n_exp;
@@ -212,13 +213,12 @@ struct Shared {
     unsigned long long ub;
 };
 
-// The random streams of the tree (ACP: 7*P, OCP: P states of 16 B) stay in dynamic shared memory for the whole launch:
-// they are read at the start of every game and written back at its end, by one thread each.
+// `n_steps` steps of tree g by the whole block, from the state the tree has in global memory and back to it.
+// The random streams of the tree (ACP: 7*P, OCP: P states of 16 B) stay in dynamic shared memory meanwhile: they are
+// read at the start of every game and written back at its end, by one thread each.
 template <bool OCP>
-__global__ void search_kernel(const SearchParams p) {
-    __shared__ Shared s;
-    extern __shared__ ulonglong2 s_rng[];
-    const int g = blockIdx.x;
+__device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulonglong2 *s_rng, const int g, const int n_steps,
+                                          const bool first) {
     const int tid = threadIdx.x;
     const int nt = blockDim.x;
     const int lane = tid & 31;
@@ -233,19 +233,9 @@ __global__ void search_kernel(const SearchParams p) {
     const int n_streams = OCP ? P : A * P;
     ulonglong2 *g_rng = p.rng_playout + (long long)g * n_streams;
     for (int i = tid; i < n_streams; i += nt) s_rng[i] = g_rng[i];
-    for (int i = tid; i < 128 * 8; i += nt) {
-        const int set = i >> 3, ord = i & 7;
-        int col = 0, seen = 0;
-        for (int c = 0; c < COLS; c++)
-            if (set & (1 << c)) {
-                if (seen == ord) col = c;
-                seen++;
-            }
-        s.move_lut[i] = (unsigned short)((7 * col) | ((1 << col) << 8));
-    }
     if (tid == 0) {
         const int b = g / p.n_trees;
-        if (p.first) {
+        if (first) {
             const int turn = p.root_turn[b];
             rec[0] = make_int4(0, 0, -1, make_meta(0, false, 2, turn, 0));
             board[0] = p.root_board[b];
@@ -281,7 +271,7 @@ __global__ void search_kernel(const SearchParams p) {
     const double c_ucb = (double)p.ucb_c;
     unsigned my_plies = 0, my_ub = 0, my_err = 0;
 
-    for (int step = 0; step < p.steps; step++) {
+    for (int step = 0; step < n_steps; step++) {
         // =========================================================== select + expand (warp 0)
         if (warp == 0) {
             int node = 0;
@@ -644,6 +634,64 @@ __global__ void search_kernel(const SearchParams p) {
         }
         for (int a = 0; a < A + 2; a++) p.actions_expanded[g * (A + 2) + a] = s.ae[a];
         for (int e = 0; e < s.path_len; e++) p.paths[g * PATH_CAP + e] = s.path[e];
+    }
+}
+
+// One block grows one tree at a time.  Without a queue block b runs the whole launch of tree b.  With a queue (batched
+// launches with more trees than blocks fit on the device) the grid is persistent and the blocks take slices of
+// p.chunk steps of whichever tree is next in the ring.
+__device__ __forceinline__ long long global_timer_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <bool OCP>
+__global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
+    __shared__ Shared s;
+    extern __shared__ ulonglong2 s_rng[];
+    const int tid = threadIdx.x;
+    for (int i = tid; i < 128 * 8; i += blockDim.x) {
+        const int set = i >> 3, ord = i & 7;
+        int col = 0, seen = 0;
+        for (int c = 0; c < COLS; c++)
+            if (set & (1 << c)) {
+                if (seen == ord) col = c;
+                seen++;
+            }
+        s.move_lut[i] = (unsigned short)((7 * col) | ((1 << col) << 8));
+    }
+    const bool queued = p.queue != nullptr;
+    for (;;) {
+        int g = blockIdx.x, rem = p.steps;
+        if (queued) {
+            if (tid == 0) s.job = queue_pop(p.queue, p.ring, p.ring_cap);
+            __syncthreads();
+            g = s.job;
+            if (g < 0) break;
+            rem = p.remaining[g];
+        }
+        const int n_steps = (queued && rem > p.chunk) ? p.chunk : rem;
+        long long t_start = 0;
+        if (queued && tid == 0) t_start = global_timer_ns();
+        run_slice<OCP>(p, s, s_rng, g, n_steps, p.first != 0 && rem == p.steps);
+        if (!queued) break;
+        __syncthreads();  // every thread's writes of the slice precede the fence of thread 0
+        if (tid == 0) {
+            const int left = rem - n_steps;
+            p.remaining[g] = left;
+            __threadfence();
+            if (left > 0) {
+                // band of the time the tree still needs at the pace of this slice, counted down from the longest whole
+                // search seen so far in this launch
+                const float us_per_step = (float)(global_timer_ns() - t_start) * 1e-3f / (float)n_steps;
+                const int whole = (int)fminf(us_per_step * (float)p.steps, 2e9f);
+                const int longest = max(atomicMax(&p.queue->longest_us, whole), max(whole, 1));
+                const float below = QUEUE_LEVELS_PER_OCTAVE * log2f((float)longest / fmaxf(us_per_step * (float)left, 1e-3f));
+                const int level = max(0, QUEUE_LEVELS - 1 - (int)fminf(fmaxf(below, 0.f), (float)QUEUE_LEVELS));
+                if (!queue_push(p.queue, p.ring, p.ring_cap, level, g)) atomicOr(&p.state[g].status, STATUS_INTERNAL);
+            }
+        }
     }
 }
 

@@ -61,6 +61,109 @@ struct TreeState {
     unsigned long long ub_draws;
 };
 
+// Work queue of a batched launch.  A tree's search is cut into slices of `chunk` steps; the blocks of a persistent grid
+// take a tree from the queue, run one slice from the state the previous slice left in global memory, and put the tree
+// back while it has steps left.  A tree is sequential, so a launch cannot end before its slowest tree (the one whose
+// games are longest) has done all its steps: the queue therefore serves the trees with the most work left first
+// (longest remaining processing time first, the rule that minimises the makespan of preemptible jobs on identical
+// machines), with the time left estimated as steps left x time per step of the slice just run.  QUEUE_LEVELS rings,
+// one per band of time left; a pop takes from the highest ring that holds a tree.
+//
+// Each ring is a bounded multi-producer multi-consumer queue with a sequence number per cell (cell i is free for the
+// push with ticket t when seq == t, holds the data of that push when seq == t + 1, and is handed to ticket t + cap by
+// the pop).  `nonempty` has one bit per ring, set after a push and cleared by a pop that found the ring empty and, after
+// clearing, still sees it empty.  Every loop is bounded and no call waits for another block: a pop that finds nothing
+// (or gives up) returns -1 and the block leaves, which is safe because a tree is always either in a ring or held by a
+// block that will publish it and pop again.
+constexpr int QUEUE_LEVELS = 64;
+constexpr float QUEUE_LEVELS_PER_OCTAVE = 6.f;  // bands are logarithmic: the estimate's error grows with the time left
+struct QueueCell {
+    int seq;
+    int tree;
+};
+struct WorkQueue {
+    int head;
+    int pad0[31];
+    int tail;
+    int pad1[31];
+};
+struct WorkQueues {
+    WorkQueue level[QUEUE_LEVELS];
+    unsigned long long nonempty;
+    int longest_us;  // longest estimate so far of a whole search's time (microseconds); the top band
+    int pad[29];
+};
+
+constexpr int QUEUE_RETRIES = 1 << 16;  // attempts of a push or pop under contention before it reports failure
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ bool ring_push(WorkQueue *q, QueueCell *ring, int cap, int tree) {
+    for (int attempt = 0; attempt < QUEUE_RETRIES; attempt++) {
+        const int pos = *(volatile int *)&q->tail;
+        QueueCell *cell = ring + (pos % cap);
+        const int dif = *(volatile int *)&cell->seq - pos;
+        if (dif == 0) {
+            if (atomicCAS(&q->tail, pos, pos + 1) == pos) {
+                *(volatile int *)&cell->tree = tree;
+                __threadfence();
+                *(volatile int *)&cell->seq = pos + 1;
+                return true;
+            }
+        } else if (dif < 0) {
+            return false;  // ring full: cannot happen while cap >= number of trees
+        }
+    }
+    return false;
+}
+
+// -1: nothing published (or QUEUE_RETRIES lost races in a row)
+__device__ __forceinline__ int ring_pop(WorkQueue *q, QueueCell *ring, int cap) {
+    for (int attempt = 0; attempt < QUEUE_RETRIES; attempt++) {
+        const int pos = *(volatile int *)&q->head;
+        QueueCell *cell = ring + (pos % cap);
+        const int dif = *(volatile int *)&cell->seq - (pos + 1);
+        if (dif == 0) {
+            if (atomicCAS(&q->head, pos, pos + 1) == pos) {
+                __threadfence();
+                const int tree = *(volatile int *)&cell->tree;
+                __threadfence();
+                *(volatile int *)&cell->seq = pos + cap;
+                return tree;
+            }
+        } else if (dif < 0) {
+            // no ticket beyond the head: empty.  Otherwise a push holds the ticket and is about to publish: look again.
+            if (*(volatile int *)&q->tail - pos <= 0) return -1;
+        }
+    }
+    return -1;
+}
+
+// the caller made the tree's state visible (block barrier after the writes, then this thread's fence) before the push
+__device__ __forceinline__ bool queue_push(WorkQueues *q, QueueCell *rings, int cap, int level, int tree) {
+    if (!ring_push(&q->level[level], rings + (long long)level * cap, cap, tree)) return false;
+    __threadfence();
+    atomicOr(&q->nonempty, 1ULL << level);
+    return true;
+}
+
+__device__ __forceinline__ int queue_pop(WorkQueues *q, QueueCell *rings, int cap) {
+    for (int attempt = 0; attempt < 8 * QUEUE_LEVELS; attempt++) {
+        const unsigned long long m = *(volatile unsigned long long *)&q->nonempty;
+        if (m == 0) return -1;
+        const int level = 63 - __clzll((long long)m);
+        WorkQueue *r = &q->level[level];
+        const int tree = ring_pop(r, rings + (long long)level * cap, cap);
+        if (tree >= 0) return tree;
+        // the ring was empty: clear its bit, then look once more; a push that slipped in between either set the bit after
+        // this clear or is seen by the second look (both sides go through read-modify-write operations and a fence)
+        atomicAnd(&q->nonempty, ~(1ULL << level));
+        __threadfence();
+        if (atomicAdd(&r->tail, 0) - atomicAdd(&r->head, 0) > 0) atomicOr(&q->nonempty, 1ULL << level);
+    }
+    return -1;
+}
+#endif
+
 struct SearchParams {
     int4 *rec;
     ulonglong2 *board;
@@ -83,6 +186,12 @@ struct SearchParams {
     int steps;               // steps to carry out in this launch
     int first;               // 1: reset the trees to the roots first (the reference's _reset)
     float ucb_c;
+    // batched launches through the work queue; queue == nullptr: block b runs all `steps` of tree b
+    WorkQueues *queue;
+    QueueCell *ring;         // [QUEUE_LEVELS][ring_cap]
+    int *remaining;          // [trees] steps of this launch a tree still has to do
+    int ring_cap;
+    int chunk;               // steps per slice
 };
 
 }  // namespace mctsnc

@@ -79,6 +79,9 @@ struct mctsnc_handle {
     ulonglong2 *rng_expand_base = nullptr;
     ulonglong2 *root_board = nullptr;
     signed char *root_turn = nullptr;
+    WorkQueues *queue = nullptr;          // Connect 4: work queue of batched launches
+    QueueCell *ring = nullptr;            // [QUEUE_LEVELS][n_trees_total]
+    int *remaining = nullptr;             // [n_trees_total]
     // Gomoku only
     unsigned *gboard = nullptr;           // [trees][cap][16]
     gomoku::StepInfo *gstep = nullptr;    // [trees]
@@ -108,6 +111,35 @@ namespace {
 
 // ---------------------------------------------------------------------------------------------------------------
 // kernels outside the search loop
+
+// fills the work queue of a batched launch with every tree once (in the highest ring: nothing is known yet about the
+// work a tree has), each with `steps` steps to do
+__global__ void init_queue_kernel(WorkQueues *q, QueueCell *rings, int *remaining, int trees, int steps) {
+    const int gsz = gridDim.x * blockDim.x;
+    const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+    for (int i = gid; i < trees * QUEUE_LEVELS; i += gsz) {
+        const int level = i / trees, c = i - level * trees;
+        const bool top = level == QUEUE_LEVELS - 1;
+        rings[i].tree = top ? c : -1;
+        rings[i].seq = top ? c + 1 : c;
+    }
+    for (int i = gid; i < trees; i += gsz) remaining[i] = steps;
+    if (gid < QUEUE_LEVELS) {  // blocks have 256 threads
+        q->level[gid].head = 0;
+        q->level[gid].tail = gid == QUEUE_LEVELS - 1 ? trees : 0;
+    }
+    if (gid == 0) {
+        q->nonempty = 1ULL << (QUEUE_LEVELS - 1);
+        q->longest_us = 0;
+    }
+}
+
+// after a queued launch: a tree that still has steps to do was lost by the queue; report it instead of returning a
+// short search
+__global__ void check_queue_kernel(const int *remaining, TreeState *state, int trees) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < trees; i += gridDim.x * blockDim.x)
+        if (remaining[i] != 0) atomicOr(&state[i].status, STATUS_INTERNAL);
+}
 
 // copies the freshly seeded streams of one search into the slots of `batch` searches
 __global__ void replicate_streams_kernel(ulonglong2 *dst, const ulonglong2 *base, long long per_search, int batch) {
@@ -451,6 +483,9 @@ void release(mctsnc_handle *h) {
     cudaFree(h->rng_expand_base);
     cudaFree(h->root_board);
     cudaFree(h->root_turn);
+    cudaFree(h->queue);
+    cudaFree(h->ring);
+    cudaFree(h->remaining);
     cudaFree(h->gboard);
     cudaFree(h->gstep);
     cudaFree(h->path_ns);
@@ -471,6 +506,11 @@ void release(mctsnc_handle *h) {
     if (h->ev0) cudaEventDestroy(h->ev0);
     if (h->ev1) cudaEventDestroy(h->ev1);
 }
+
+#ifndef MCTSNC_SLICE_STEPS
+#define MCTSNC_SLICE_STEPS 32
+#endif
+constexpr int SLICE_STEPS = MCTSNC_SLICE_STEPS;  // steps a block runs of one tree before it takes the next tree from the queue
 
 const void *search_kernel_ptr(const mctsnc_config &c) {
     return is_ocp(c) ? (const void *)c4::search_kernel<true> : (const void *)c4::search_kernel<false>;
@@ -611,8 +651,33 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
     const long long trees = (long long)batch * h->cfg.n_trees;
     const int threads = h->cfg.threads_per_tree > 0 ? h->cfg.threads_per_tree : choose_threads(h, trees);
     h->threads = threads;
-    if (is_ocp(h->cfg)) c4::search_kernel<true><<<(unsigned)trees, threads, h->dyn_smem, stream>>>(p);
-    else c4::search_kernel<false><<<(unsigned)trees, threads, h->dyn_smem, stream>>>(p);
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, search_kernel_ptr(h->cfg), threads, h->dyn_smem) != cudaSuccess || per_sm < 1)
+        return MCTSNC_E_BAD_ARGUMENT;
+    h->blocks_per_sm = per_sm;
+    // More trees than blocks fit on the device at once: a persistent grid takes slices of SLICE_STEPS steps from the
+    // work queue, so that trees with long games do not keep a few SMs busy after the others have run out of work
+    // (measured on 1024 trees of 2000 steps: 11.1 G playouts/s with one block per tree, see the design notes for the
+    // queued figure).  Otherwise block b grows tree b for the whole launch.
+    const long long resident = (long long)per_sm * h->sm_count;
+    unsigned grid = (unsigned)trees;
+    p.queue = nullptr;
+    p.ring = nullptr;
+    p.remaining = nullptr;
+    p.ring_cap = 0;
+    p.chunk = 0;
+    if (trees > resident && steps > SLICE_STEPS) {
+        init_queue_kernel<<<(unsigned)((trees + 255) / 256), 256, 0, stream>>>(h->queue, h->ring, h->remaining, (int)trees, steps);
+        p.queue = h->queue;
+        p.ring = h->ring;
+        p.remaining = h->remaining;
+        p.ring_cap = (int)trees;
+        p.chunk = SLICE_STEPS;
+        grid = (unsigned)resident;
+    }
+    if (is_ocp(h->cfg)) c4::search_kernel<true><<<grid, threads, h->dyn_smem, stream>>>(p);
+    else c4::search_kernel<false><<<grid, threads, h->dyn_smem, stream>>>(p);
+    if (p.queue) check_queue_kernel<<<(unsigned)((trees + 255) / 256), 256, 0, stream>>>(h->remaining, h->state, (int)trees);
     return (int)cudaGetLastError();
 }
 
@@ -758,6 +823,9 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc) rc = dev_alloc(h, &h->rng_expand_base, (long long)c.n_trees);
     if (!rc) rc = dev_alloc(h, &h->root_board, (long long)c.max_batch);
     if (!rc) rc = dev_alloc(h, &h->root_turn, (long long)c.max_batch);
+    if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->queue, 1);
+    if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->ring, h->n_trees_total * QUEUE_LEVELS);
+    if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->remaining, h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->sums, (long long)c.max_batch * 3 * h->A);
     if (!rc) rc = dev_alloc(h, &h->flags, (long long)c.max_batch * 2 * h->A);
     if (!rc) rc = dev_alloc(h, &h->dres, (long long)c.max_batch);
@@ -1282,6 +1350,11 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
     p.steps = (int)steps;
     p.first = 1;
     p.ucb_c = ucb_c;
+    p.queue = nullptr;
+    p.ring = nullptr;
+    p.remaining = nullptr;
+    p.ring_cap = 0;
+    p.chunk = 0;
     const size_t dyn_smem = sizeof(ulonglong2) * (size_t)per_tree;   // <= 28 KB: below the 48 KB that need an opt-in
     if (ocp) c4::search_kernel<true><<<n_trees, 256, dyn_smem, s>>>(p);
     else c4::search_kernel<false><<<n_trees, 256, dyn_smem, s>>>(p);

@@ -408,6 +408,21 @@ class MCTSNC:
                "trees_selected_paths": (12, np.int32), "trees_actions_expanded": (13, np.int16),
                "trees_playout_outcomes": (14, np.int32), "trees_playout_outcomes_children": (15, np.int32)}
 
+    SLICE_STEPS = 32  # steps a block runs of one tree before it takes another from the work queue (batched launches)
+
+    def launch_geometry(self):
+        """Geometry of the last search launch: threads per tree, resident blocks per SM, SMs of the device and the bytes
+        of device memory the handle holds.  A Connect-4 batch with more trees than ``blocks_per_sm * sm_count`` and more
+        than ``SLICE_STEPS`` steps runs as a persistent grid fed by the work queue."""
+        if self._handle is None:
+            raise RuntimeError("[MCTSNC: init_device_side_arrays() has to be called first]")
+        i32, i64 = ctypes.c_int32, ctypes.c_int64
+        thr, per_sm, sms, nbytes = i32(0), i32(0), i32(0), i64(0)
+        _abi.check(_abi.lib().mctsnc_query(self._handle, ctypes.byref(thr), ctypes.byref(per_sm), ctypes.byref(sms),
+                                           ctypes.byref(nbytes)))
+        return {"threads_per_tree": thr.value, "blocks_per_sm": per_sm.value, "sm_count": sms.value,
+                "device_bytes": nbytes.value}
+
     def export(self, name, search=0, max_nodes=None):
         """Device arrays of the last run in the reference's formats (what ``_json_dump`` copies to the host)."""
         fid, dtype = self._EXPORT[name]

@@ -216,3 +216,33 @@ def test_tree_full_is_reported_not_followed():
     assert (sizes <= 40).all() and (sizes > 30).all()
     ns = ai.export("trees_ns", max_nodes=40)
     assert (ns[:, 0] > 0).all() and ai.steps == 100
+
+
+@pytest.mark.parametrize("variant", ["acp_prodigal", "ocp_thrifty"])
+def test_queued_batch_matches_oracle(variant):
+    """More trees than blocks fit on the device: a persistent grid takes 32-step slices of the trees from the work queue
+    (whichever tree has most time left first).  Every tree must come out as if it had been grown in one go."""
+    B, T, P, steps = 200, 4, 32, 75       # 800 trees; slices of 32, 32 and 11 steps
+    boards, fills, turns = c4_random_roots(B, 20, seed=5)
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=T, n_playouts=P, variant=variant,
+                seed=4, verbose_info=False, max_batch=B)
+    ai.init_device_side_arrays()
+    out = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    geo = ai.launch_geometry()
+    assert B * T > geo["blocks_per_sm"] * geo["sm_count"] and steps > MCTSNC.SLICE_STEPS   # the queue was used
+    assert (out["status"] & _abi.STATUS_INTERNAL == 0).all()
+    assert (out["steps"] == steps).all()
+    again = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    for name in ("best_action", "best_n", "best_n_wins", "playouts", "plies", "actions_ns", "actions_ns_wins", "root_ns"):
+        assert np.array_equal(out[name], again[name]), name
+    for b in (0, 57, 123, 199):
+        orc = OracleMCTSNC((6, 7), 7, 7, n_trees=T, n_playouts=P, variant=variant, seed=4, node_capacity=steps * 7 + 8)
+        orc.run(boards[b], fills[b], int(turns[b]), steps)
+        compare_trees(ai, orc, search=b)
+        assert out["best_action"][b] == orc.best_action
+        assert out["best_n"][b] == orc.best_n and out["best_n_wins"][b] == orc.best_n_wins
+        assert out["playouts"][b] == orc.playouts and out["plies"][b] == orc.plies
+    # the same roots a few at a time (one block per tree, no queue) give the same searches
+    few = ai.run_batch(boards[:8], fills[:8], turns[:8], steps=steps, reseed=True)
+    for name in ("best_action", "best_n", "best_n_wins", "actions_ns", "actions_ns_wins"):
+        assert np.array_equal(out[name][:8], few[name]), name
