@@ -20,6 +20,7 @@ namespace mctsnc {
 namespace c4 {
 
 constexpr int ROWS = 6, COLS = 7, A = 7;
+constexpr int PLIES_PER_CHECK = 4;  // plies of a playout between two looks at whether the game is over
 constexpr unsigned long long BOTTOM_ROW = 0x0000040810204081ULL;  // bit 7c for c = 0..6
 constexpr unsigned long long TOP_ROW = BOTTOM_ROW << 5;
 constexpr unsigned long long FULL_BOARD = BOTTOM_ROW * 0x3FULL;
@@ -479,42 +480,51 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 s1 = rs.y;
             }
             while (item < n_items) {
-                // ---- one ply (src/mctsnc.py:2059-2064, :2069)
-                const float u = rng_uniform_f32(s0, s1);
-                const float prod = __fmul_rn(u, count);  // float32 * int16 -> float32 (:2061)
-                bool win, over;
+                // A finished game is noticed only every PLIES_PER_CHECK plies: its lane sits out the plies in between.  The
+                // code that closes a game and fetches the next one (about 30 instructions) runs for the few lanes whose
+                // games have just ended while the others wait, and with a check after every ply it ran in nearly every
+                // iteration; checking after every fourth ply costs a little lane time and saved 10 % of the run time
+                // (13.8 -> 15.3 G playouts/s on the headline workload; 2: 14.9, 3: 15.3, 5: 15.4, 8: 14.1).
+                bool win = false, over = false;
                 int emu_outcome = 2;
-                if (prod >= count) {
-                    // u == 1.0f: replay this game through the byte-level emulation of the reference
-                    const GameSlot gs = s.slot[j];
-                    const ulonglong2 rs = s_rng[rng_idx];
-                    const unsigned long long other = gs.all ^ gs.cur;
-                    const EmuResult er = playout_emulated(first_mover > 0 ? other : gs.cur, first_mover > 0 ? gs.cur : other,
-                                                          first_mover, rs.x, rs.y);
-                    s0 = er.s0;
-                    s1 = er.s1;
-                    emu_outcome = er.outcome;
-                    my_plies += er.plies;
-                    my_ub += er.ub;
-                    my_err |= er.err;
-                    all = 0;  // the plies of the replay are counted above, none from the bitboards
-                    stones = 0;
-                    win = false;
-                    over = true;
-                } else {
-                    const int ord = __float2int_rz(prod);
-                    const unsigned e = s.move_lut[legal * 8 + ord];
-                    const unsigned long long nall = all | (all + (1ULL << (e & 0xFF)));
-                    const unsigned long long move = nall ^ all;
-                    const unsigned long long mine = cur | move;
-                    cur = all ^ cur;
-                    all = nall;
-                    win = has_four(mine);
-                    if ((move & TOP_ROW) != 0) {
-                        legal ^= e >> 8;
-                        count -= 1.0f;
+#pragma unroll
+                for (int k = 0; k < PLIES_PER_CHECK; k++) {
+                    if (over) continue;
+                    // ---- one ply (src/mctsnc.py:2059-2064, :2069)
+                    const float u = rng_uniform_f32(s0, s1);
+                    const float prod = __fmul_rn(u, count);  // float32 * int16 -> float32 (:2061)
+                    if (prod >= count) {
+                        // u == 1.0f: replay this game through the byte-level emulation of the reference
+                        const GameSlot gs = s.slot[j];
+                        const ulonglong2 rs = s_rng[rng_idx];
+                        const unsigned long long other = gs.all ^ gs.cur;
+                        const EmuResult er = playout_emulated(first_mover > 0 ? other : gs.cur, first_mover > 0 ? gs.cur : other,
+                                                              first_mover, rs.x, rs.y);
+                        s0 = er.s0;
+                        s1 = er.s1;
+                        emu_outcome = er.outcome;
+                        my_plies += er.plies;
+                        my_ub += er.ub;
+                        my_err |= er.err;
+                        all = 0;  // the plies of the replay are counted above, none from the bitboards
+                        stones = 0;
+                        win = false;
+                        over = true;
+                    } else {
+                        const int ord = __float2int_rz(prod);
+                        const unsigned e = s.move_lut[legal * 8 + ord];
+                        const unsigned long long nall = all | (all + (1ULL << (e & 0xFF)));
+                        const unsigned long long move = nall ^ all;
+                        const unsigned long long mine = cur | move;
+                        cur = all ^ cur;
+                        all = nall;
+                        win = has_four(mine);
+                        if ((move & TOP_ROW) != 0) {
+                            legal ^= e >> 8;
+                            count -= 1.0f;
+                        }
+                        over = win || count == 0.0f;
                     }
-                    over = win || count == 0.0f;
                 }
                 if (over) {
                     s_rng[rng_idx] = make_ulonglong2(s0, s1);
