@@ -20,7 +20,11 @@ namespace mctsnc {
 namespace c4 {
 
 constexpr int ROWS = 6, COLS = 7, A = 7;
-constexpr int PLIES_PER_CHECK = 4;  // plies of a playout between two looks at whether the game is over
+constexpr int LEGAL_SHIFT = 6;       // the playout loop keeps the set of open columns times 64 = byte offset of its row of move_lut
+#ifndef MCTSNC_PLIES_PER_CHECK
+#define MCTSNC_PLIES_PER_CHECK 4
+#endif
+constexpr int PLIES_PER_CHECK = MCTSNC_PLIES_PER_CHECK;  // plies of a playout between two looks at whether the game is over
 constexpr unsigned long long BOTTOM_ROW = 0x0000040810204081ULL;  // bit 7c for c = 0..6
 constexpr unsigned long long TOP_ROW = BOTTOM_ROW << 5;
 constexpr unsigned long long FULL_BOARD = BOTTOM_ROW * 0x3FULL;
@@ -175,10 +179,10 @@ __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsig
 struct __align__(16) GameSlot {
     unsigned long long cur;  // stones of the side to move
     unsigned long long all;  // all stones
-    unsigned legal;          // columns with room
+    unsigned legal;          // columns with room, shifted left by LEGAL_SHIFT
     int rng_base;            // index of the child's first stream in the block's stream array
     int stones;              // stones on the board
-    float count;             // number of columns with room
+    float count;             // number of columns with room times 2^-64 (the playout loop draws uniforms scaled by 2^64)
 };
 
 struct Shared {
@@ -192,9 +196,10 @@ struct Shared {
     int child_slot[A];       // and its slot (-1: no playouts: terminal, or not picked in OCP)
     int child_out[A][2];     // trees_playout_outcomes_children (persists over steps)
     short ae[A + 2];         // trees_actions_expanded row (persists over steps)
-    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the bit position of the
-    // column's bottom cell (7 * column) in the low byte and the column's bit (1 << column) in the high byte
-    unsigned short move_lut[128 * 8];
+    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the bottom cell of the column
+    // (bit 7 * column) in bits 0..47 and the column's bit in bits 54..60, i.e. where it sits in the pre-shifted column
+    // set the playout loop keeps (GameSlot::legal), moved up by 48
+    unsigned long long move_lut[128 * 8];
     int job;                 // tree of the slice being run (-1: none left)
     int n_slots;
     int next_item;           // next game to hand out in the playout phase
@@ -391,10 +396,10 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                             GameSlot gs;
                             gs.cur = sel_turn > 0 ? cneg : cpos;  // the child is to be moved in by the other side
                             gs.all = call;
-                            gs.legal = legal_columns(call);
+                            gs.legal = legal_columns(call) << LEGAL_SHIFT;
                             gs.rng_base = OCP ? 0 : lane * P;
                             gs.stones = __popcll(call);
-                            gs.count = (float)__popc(gs.legal);
+                            gs.count = (float)__popc(gs.legal) * RNG_2M64;
                             s.slot[j] = gs;
                             s.tally[j][0] = 0;
                             s.tally[j][1] = 0;
@@ -408,10 +413,10 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         GameSlot gs;
                         gs.cur = sel_turn > 0 ? bb.y : bb.x;
                         gs.all = all;
-                        gs.legal = legal;
+                        gs.legal = legal << LEGAL_SHIFT;
                         gs.rng_base = 0;
                         gs.stones = __popcll(all);
-                        gs.count = (float)n_legal;
+                        gs.count = (float)n_legal * RNG_2M64;
                         s.slot[0] = gs;
                         s.tally[0][0] = 0;
                         s.tally[0][1] = 0;
@@ -461,7 +466,9 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             // the side to move in the played-out positions: the other side than at the selected node, unless the
             // selected node itself is played out
             const int first_mover = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
-            unsigned long long cur = 0, all = 0, s0 = 0, s1 = 0;
+            // stones of the side that moves at the even plies of a block of PLIES_PER_CHECK plies (a game starts at ply 0 of a
+            // block, so that is the side to move in the game's first position), stones of the other side, all stones
+            unsigned long long side_even = 0, side_odd = 0, all = 0, s0 = 0, s1 = 0;
             unsigned legal = 0;
             float count = 0.f;
             int rng_idx = 0, stones = 0, j = 0;
@@ -469,7 +476,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             if (item < n_items) {
                 j = item >> p.log2_playouts;
                 const GameSlot gs = s.slot[j];
-                cur = gs.cur;
+                side_even = gs.cur;
+                side_odd = gs.all ^ gs.cur;
                 all = gs.all;
                 legal = gs.legal;
                 count = gs.count;
@@ -487,13 +495,15 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 // (13.8 -> 15.3 G playouts/s on the headline workload; 2: 14.9, 3: 15.3, 5: 15.4, 8: 14.1).
                 bool win = false, over = false;
                 int emu_outcome = 2;
+                static_assert(PLIES_PER_CHECK % 2 == 0, "the two sides alternate by the parity of the ply within a block");
 #pragma unroll
                 for (int k = 0; k < PLIES_PER_CHECK; k++) {
                     if (over) continue;
                     // ---- one ply (src/mctsnc.py:2059-2064, :2069)
-                    const float u = rng_uniform_f32(s0, s1);
-                    const float prod = __fmul_rn(u, count);  // float32 * int16 -> float32 (:2061)
-                    if (prod >= count) {
+                    // float32 u * int16 count -> float32 (:2061); here (u * 2^64) * (count * 2^-64): the same product
+                    const float f = rng_uniform_times_2p64(s0, s1);
+                    const float prod = __fmul_rn(f, count);
+                    if (f >= RNG_2P64) {
                         // u == 1.0f: replay this game through the byte-level emulation of the reference
                         const GameSlot gs = s.slot[j];
                         const ulonglong2 rs = s_rng[rng_idx];
@@ -512,16 +522,24 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         over = true;
                     } else {
                         const int ord = __float2int_rz(prod);
-                        const unsigned e = s.move_lut[legal * 8 + ord];
-                        const unsigned long long nall = all | (all + (1ULL << (e & 0xFF)));
+                        const unsigned long long e = *reinterpret_cast<const unsigned long long *>(
+                            reinterpret_cast<const char *>(s.move_lut) + (legal + ord * 8));
+                        const unsigned long long nall = all | (all + (e & 0x0000FFFFFFFFFFFFULL));
                         const unsigned long long move = nall ^ all;
-                        const unsigned long long mine = cur | move;
-                        cur = all ^ cur;
+                        // the sides take turns with the plies of the unrolled block: no swap of "mine" and "theirs"
+                        unsigned long long mine;
+                        if (k & 1) {
+                            side_odd |= move;
+                            mine = side_odd;
+                        } else {
+                            side_even |= move;
+                            mine = side_even;
+                        }
                         all = nall;
                         win = has_four(mine);
                         if ((move & TOP_ROW) != 0) {
-                            legal ^= e >> 8;
-                            count -= 1.0f;
+                            legal ^= (unsigned)(e >> 48);
+                            count -= RNG_2M64;
                         }
                         over = win || count == 0.0f;
                     }
@@ -537,7 +555,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                     if (item < n_items) {
                         j = item >> p.log2_playouts;
                         const GameSlot gs = s.slot[j];
-                        cur = gs.cur;
+                        side_even = gs.cur;
+                        side_odd = gs.all ^ gs.cur;
                         all = gs.all;
                         legal = gs.legal;
                         count = gs.count;
@@ -669,7 +688,7 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
                 if (seen == ord) col = c;
                 seen++;
             }
-        s.move_lut[i] = (unsigned short)((7 * col) | ((1 << col) << 8));
+        s.move_lut[i] = (1ULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
     }
     const bool queued = p.queue != nullptr;
     for (;;) {

@@ -58,6 +58,16 @@ __device__ __forceinline__ float rng_uniform_f32(unsigned long long &s0, unsigne
     unsigned long long x = rng_next(s0, s1);
     return __fmul_rn(__ull2float_rn(x >> 11), 1.1102230246251565e-16f);
 }
+
+// The same uniform scaled by 2^64, for callers that fold the scaling into a constant of their own: clearing the low 11
+// bits instead of shifting them out gives (x >> 11) * 2^11, whose conversion rounds exactly like that of x >> 11
+// (a power-of-two factor moves no rounding boundary, and 2^64 is representable), so
+// rng_uniform_f32() == rng_uniform_times_2p64() * 2^-64 bit for bit; the value 2^64 stands for 1.0f.
+constexpr float RNG_2P64 = 18446744073709551616.f;
+constexpr float RNG_2M64 = 5.421010862427522e-20f;
+__device__ __forceinline__ float rng_uniform_times_2p64(unsigned long long &s0, unsigned long long &s1) {
+    return __ull2float_rn(rng_next(s0, s1) & ~0x7FFULL);
+}
 #endif
 
 }  // namespace mctsnc
