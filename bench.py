@@ -34,7 +34,7 @@ GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0,
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one search-kernel launch, from a one-pass ncu capture of the default
 # workload; key: game, variant, trees, playouts, search steps, roots
-MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 126915584 + 405630208}
+MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 133639424 + 409819136}
 
 
 def parse_args():
