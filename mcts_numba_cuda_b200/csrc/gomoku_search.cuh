@@ -727,36 +727,48 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 const unsigned row = my[(LIST_WORDS + i) * DYN_THREADS] | (1u << (hs + j));
                 my[(LIST_WORDS + i) * DYN_THREADS] = row;
                 plies++;
+                // compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) without data-dependent loops: for each of the
+                // four directions the mover's stones on the line through (i, j) are gathered into a window with the new
+                // stone at bit 15 and the cell r steps "down" the line at bit 15 + r (15 - r for the anti-diagonal), five
+                // cells either way for the directions that cross rows; the runs next to bit 15 are then counted with
+                // find-first-set / count-leading-zeros.  The reference counts at most 5 stones either way and wants a total of
+                // exactly 4, which holds iff the two runs add up to 4.  Rows outside the board are not masked when they are
+                // read (the words fetched in their place are this thread's own list words, or row 14 again): a run is cut
+                // to the number of rows that exist on its side instead.
                 bool win;
                 {
-                    const unsigned m = (row >> hs) & 0x7FFFu;
-                    int total = 0;
-                    for (int d = 1; d < 6; d++) {
-                        if (j + d >= N || !((m >> (j + d)) & 1u)) break;
-                        total++;
-                    }
-                    for (int d = 1; d < 6; d++) {
-                        if (j - d < 0 || !((m >> (j - d)) & 1u)) break;
-                        total++;
-                    }
-                    win = total == 4;
-                }
-                if (!win) {
+                    const unsigned *my_row = my + (LIST_WORDS + i) * DYN_THREADS;
+                    // column c of the mover's half of a row word goes to bit 15 + c - j: one rotation, by 17 + j for the
+                    // half at bits 0..14 (a left shift by 15 - j) and by 1 + j for the half at bits 16..30; the 15 masked
+                    // bits never wrap around
+                    const unsigned half = 0x7FFFu << hs;
+                    const int rot = (17 + j + hs) & 31;
+                    unsigned gh = __funnelshift_r(row & half, row & half, rot);
+                    unsigned gv = 0, gd = 0, ga = 0;
 #pragma unroll
-                    for (int dir = -1; dir <= 1 && !win; dir++) {
-                        int total = 0;
-                        for (int d = 1; d < 6; d++) {
-                            const int ii = i + d, jj = j + dir * d;
-                            if (ii >= M || jj < 0 || jj >= N || !((my[(LIST_WORDS + ii) * DYN_THREADS] >> (hs + jj)) & 1u)) break;
-                            total++;
-                        }
-                        for (int d = 1; d < 6; d++) {
-                            const int ii = i - d, jj = j - dir * d;
-                            if (ii < 0 || jj < 0 || jj >= N || !((my[(LIST_WORDS + ii) * DYN_THREADS] >> (hs + jj)) & 1u)) break;
-                            total++;
-                        }
-                        win = total == 4;
+                    for (int r = 1; r <= 5; r++) {
+                        // r rows up: row i - r
+                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;
+                        const unsigned up = __funnelshift_r(up_w, up_w, rot);
+                        gv |= (up >> r) & (1u << (15 - r));
+                        gd |= up & (1u << (15 - r));          // (i - r, j - r)
+                        ga |= up & (1u << (15 + r));          // (i - r, j + r)
+                        // r rows down: row i + r (row 14 again beyond the board; the run is cut below)
+                        const int rd = min(i + r, M - 1);
+                        const unsigned dn_w = my[(LIST_WORDS + rd) * DYN_THREADS] & half;
+                        const unsigned dn = __funnelshift_r(dn_w, dn_w, rot);
+                        gv |= (dn << r) & (1u << (15 + r));
+                        gd |= dn & (1u << (15 + r));          // (i + r, j + r)
+                        ga |= dn & (1u << (15 - r));          // (i + r, j - r)
                     }
+                    const int rows_up = i, rows_dn = M - 1 - i;
+                    // stones next to bit 15: towards higher bits (trailing ones of g >> 16), towards lower bits (leading ones
+                    // of g << 17)
+                    const int h_hi = __ffs(~(gh >> 16)) - 1, h_lo = __clz(~(gh << 17));
+                    const int v_hi = min(__ffs(~(gv >> 16)) - 1, rows_dn), v_lo = min(__clz(~(gv << 17)), rows_up);
+                    const int d_hi = min(__ffs(~(gd >> 16)) - 1, rows_dn), d_lo = min(__clz(~(gd << 17)), rows_up);
+                    const int a_hi = min(__ffs(~(ga >> 16)) - 1, rows_up), a_lo = min(__clz(~(ga << 17)), rows_dn);
+                    win = (h_hi + h_lo == 4) | (v_hi + v_lo == 4) | (d_hi + d_lo == 4) | (a_hi + a_lo == 4);
                 }
                 if (win) outcome = turn;
                 else if (count == 0) outcome = 0;

@@ -516,27 +516,30 @@ const void *search_kernel_ptr(const mctsnc_config &c) {
     return is_ocp(c) ? (const void *)c4::search_kernel<true> : (const void *)c4::search_kernel<false>;
 }
 
-// threads of the block that grows one tree.  Many trees (throughput regime, at least two per SM): 384, the best
-// of a measured sweep 96..512 on the headline workload (the kernel is bound by the integer pipe, block size matters
-// by less than 10 %).
+// Threads of the block that grows one tree, from the games a step plays (n_playouts, times the children of a node for
+// the ACP variants) and from how many trees there are for the device.
+//   Many trees (at least two per SM): a quarter of the games, between 32 and 384.  Measured on 256 roots: headline ACP
+//   4 x 256 (1792 games a step) 15.2 / 15.4 / 15.1-16.8 G playouts/s at 256 / 320 / 384 threads, 14.1 at 512; OCP 8 trees
+//   x 1000 steps with 32 / 128 / 512 playouts: 4.2 / 8.2 / 17.7 G/s at 32 / 64 / 128 threads against 1.4 / 5.0 / 12.8 at
+//   384 (small blocks put more trees on an SM, which hides the latency of the select/expand/backup warp).
+//   Few trees (a tree has an SM to itself): one thread per game, at most 1024; measured on one 4-tree ACP search of
+//   2000 steps: 94.7 ms with 256 threads, 69.3 ms with 512, 67.5 ms with 1024.  In between: half the games, at most 512.
 int choose_threads(mctsnc_handle *h, long long trees) {
+    const int games = h->cfg.n_playouts * (is_ocp(h->cfg) ? 1 : h->A);
+    auto fit = [](int want, int most) {
+        const int t = (want + 31) / 32 * 32;
+        return t < 32 ? 32 : (t > most ? most : t);
+    };
+    int threads;
+    if (trees >= 2LL * h->sm_count) threads = fit(games / 4, 384);
+    else if (trees <= h->sm_count) threads = fit(games, 1024);
+    else threads = fit(games / 2, 512);
     const void *fn = search_kernel_ptr(h->cfg);
     int per_sm = 0;
-    if (trees >= 2LL * h->sm_count) {
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 384, h->dyn_smem);
-        h->blocks_per_sm = per_sm;
-        return 384;
-    }
-    // Few trees (latency regime): a tree has an SM to itself, so give it as many threads as a block can have; measured
-    // on one 4-tree search of 2000 steps: 94.7 ms with 256 threads, 69.3 ms with 512, 67.5 ms with 1024.
-    const int threads = trees <= h->sm_count ? 1024 : 512;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, h->dyn_smem) == cudaSuccess && per_sm >= 1) {
-        h->blocks_per_sm = per_sm;
-        return threads;
-    }
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, 256, h->dyn_smem);
-    h->blocks_per_sm = per_sm;
-    return 256;
+    while (threads > 32 &&
+           (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, h->dyn_smem) != cudaSuccess || per_sm < 1))
+        threads -= 32;
+    return threads;
 }
 
 int seed_streams(mctsnc_handle *h, int batch, cudaStream_t stream) {

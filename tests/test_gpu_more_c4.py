@@ -225,7 +225,7 @@ def test_queued_batch_matches_oracle(variant):
     B, T, P, steps = 200, 4, 32, 75       # 800 trees; slices of 32, 32 and 11 steps
     boards, fills, turns = c4_random_roots(B, 20, seed=5)
     ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=T, n_playouts=P, variant=variant,
-                seed=4, verbose_info=False, max_batch=B)
+                seed=4, verbose_info=False, max_batch=B, threads_per_tree=384)   # large blocks: fewer fit than there are trees
     ai.init_device_side_arrays()
     out = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
     geo = ai.launch_geometry()
