@@ -43,13 +43,14 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="search", choices=["search", "puct"],
+    ap.add_argument("--workload", default="search", choices=["search", "puct", "duct"],
                     help="search: the MCTS-NC search (headline); puct: the warp-level PUCT select (BASELINE config 5)")
     ap.add_argument("--puct-trees", type=int, default=4096)
     ap.add_argument("--puct-edges", type=int, default=64)
     ap.add_argument("--puct-depth", type=int, default=16)
     ap.add_argument("--puct-warps", type=int, default=8)
     ap.add_argument("--puct-virtual-loss", type=int, default=3)
+    ap.add_argument("--duct-actions", type=int, default=8, help="actions per player of the decoupled-UCT workload")
     ap.add_argument("--game", default="c4", choices=sorted(GAMES))
     ap.add_argument("--roots", type=int, default=256)
     ap.add_argument("--search-steps", type=int, default=2000)
@@ -284,10 +285,106 @@ def run_puct(args):
     print(json.dumps(line))
 
 
+def duct_device_case(trees, actions, depth, warps, seed, device):
+    """Layered trees for the decoupled-UCT select, generated on the device: level l+1 holds A*A nodes shared by the nodes
+    of level l (child of joint action j of the i-th node of a level = node (i + j) % (A*A) of the next), the last level is
+    terminal; priors ~ Dirichlet(0.3) per player, joint visit counts ~ U{0..49} and joint value sums N * U[-1, 1], from
+    which the per-player marginals are summed (player 1's value sums are the negatives)."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    A, per = actions, actions * actions
+    nodes = 1 + per * depth
+    level_of = torch.zeros(nodes, dtype=torch.long, device=device)
+    level_of[1:] = (torch.arange(nodes - 1, device=device) // per) + 1
+    idx_in_level = torch.zeros(nodes, dtype=torch.long, device=device)
+    idx_in_level[1:] = torch.arange(nodes - 1, device=device) % per
+    nxt = 1 + per * level_of[:, None] + (torch.arange(per, device=device)[None, :] + idx_in_level[:, None]) % per
+    nxt[level_of == depth] = -1
+    gamma = torch._standard_gamma(torch.full((trees, nodes, 2, A), 0.3, device=device), generator=g)
+    prior = (gamma / gamma.sum(dim=3, keepdim=True).clamp_min(1e-30)).float()
+    nj = torch.randint(0, 50, (trees, nodes, A, A), device=device, generator=g, dtype=torch.int32)
+    wj = nj.float() * (torch.rand((trees, nodes, A, A), device=device, generator=g) * 2 - 1)
+    node_n = torch.stack([nj.sum(dim=3), nj.sum(dim=2)], dim=2).to(torch.int32)
+    node_w = torch.stack([wj.sum(dim=3), -wj.sum(dim=2)], dim=2).float()
+    terminal = (level_of == depth).to(torch.int32)
+    return {"child": nxt.to(torch.int32)[None].expand(trees, -1, -1).contiguous(), "node_prior": prior.contiguous(),
+            "node_w": node_w.contiguous(), "node_n": node_n.contiguous(),
+            "node_inflight": torch.zeros((trees, nodes, 2, A), dtype=torch.int32, device=device),
+            "node_terminal": terminal[None].expand(trees, -1).contiguous(),
+            "node_count": torch.full((trees,), nodes, dtype=torch.int32, device=device),
+            "out_selected": torch.zeros((trees, warps), dtype=torch.int32, device=device),
+            "out_path": torch.full((trees, warps, depth + 1), -1, dtype=torch.int32, device=device),
+            "out_len": torch.zeros((trees, warps), dtype=torch.int32, device=device), "trees": trees, "warps": warps}
+
+
+def run_duct(args):
+    """Decoupled-UCT select for 2 players x A actions (no counterpart in the reference; the specification is the one of
+    include/duct_b200.h): select-only timing as for PUCT, an untimed release after each launch; the CPU baseline is the
+    numpy restatement on a sample of the same trees."""
+    import torch
+    from mcts_numba_cuda_b200 import _abi, duct
+    from mcts_numba_cuda_b200.puct import to_host
+    _abi.lib()
+    dev = "cuda:0"
+    T, A, D, Wp, vl = args.puct_trees, args.duct_actions, args.puct_depth, args.puct_warps, args.puct_virtual_loss
+    d = duct_device_case(T, A, D, Wp, 0, dev)
+    pk = peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    times = []
+    for i in range(args.warmup + args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        duct.launch_select(d, cpuct=1.5, virtual_loss=vl)
+        e1.record()
+        torch.cuda.synchronize()
+        kinds = (d["out_selected"] >> 22) & 7
+        mean_len = float(d["out_len"].float().mean())
+        duct.launch_backup(d, None, None, virtual_loss=vl)
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+    assert int(d["node_inflight"].abs().sum()) == 0
+    clocks = sampler.stop()
+    ms = float(np.mean(times))
+    sel = T * Wp
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import duct_oracle as do
+        sample = min(T, 1024)
+        h = {k: (v[:sample].cpu().numpy() if hasattr(v, "cpu") else v) for k, v in d.items()}
+        h["trees"] = sample
+        t0 = time.perf_counter()
+        do.select(h, cpuct=1.5, virtual_loss=vl)
+        dt = time.perf_counter() - t0
+        cpu = {"value": sample * Wp / dt, "unit": "selections/s", "cores": 1, "kind": "port",
+               "sample": f"{sample} of the {T} trees x {Wp} warps, sequential numpy restatement, {dt:.1f} s"}
+    bytes_per_sel = mean_len * (2 * A * 16 + A * A * 4 + 4) + 16
+    achieved = sel * bytes_per_sel / (ms * 1e-3) / 1e9
+    line = {"metric": "DUCT selections/sec (select kernel only, CUDA events)", "value": sel / (ms * 1e-3), "unit": "selections/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"decoupled-UCT select, 2 players x {A} actions: {T} trees, layered depth {D}, {Wp} warps per "
+                                   f"tree, virtual loss {vl}, c_puct 1.5, priors ~ Dirichlet(0.3); no counterpart in the reference",
+                       "l2": f"node arrays {T * (1 + A * A * D) * (2 * A * 16 + A * A * 4) / 1e9:.1f} GB exceed the 126 MB L2"},
+            "mean_path_length": mean_len, "busy_fraction": float((kinds == 4).float().mean()),
+            "e2e": {"value": sel / (ms * 1e-3), "unit": "selections/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "trees live on the device; a select has no host input"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                         "kernel": "duct::select_kernel", "bytes_per_selection": bytes_per_sel},
+            "cpu_baseline": cpu, "gpu_launches": 2 * (args.steps + args.warmup), "clocks": clocks}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
     if args.workload == "puct":
         run_puct(args)
+        return
+    if args.workload == "duct":
+        run_duct(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

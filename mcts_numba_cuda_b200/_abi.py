@@ -26,6 +26,8 @@ EXPORTED = ["mctsnc_create", "mctsnc_destroy", "mctsnc_reset_rng", "mctsnc_run",
 # the PUCT entry points keep the names of the reference's native library (include/puct_b200.h)
 EXPORTED_PUCT = ["puct_select_winner_recalc_launch", "puct_select_virtual_loss_launch", "puct_backup_launch",
                  "puct_cpp_cuda_error_string"]
+# decoupled-UCT select for simultaneous moves: no counterpart in the reference (include/duct_b200.h)
+EXPORTED_DUCT = ["duct_select_launch", "duct_backup_launch"]
 
 
 class Config(ctypes.Structure):

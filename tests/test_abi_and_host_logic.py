@@ -23,7 +23,8 @@ def declared_functions(header, prefix):
 
 def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(_abi.LIB_PATH)
-    for header, prefix, listed in (("mctsnc_b200.h", "mctsnc", _abi.EXPORTED), ("puct_b200.h", "puct", _abi.EXPORTED_PUCT)):
+    for header, prefix, listed in (("mctsnc_b200.h", "mctsnc", _abi.EXPORTED), ("puct_b200.h", "puct", _abi.EXPORTED_PUCT),
+                                   ("duct_b200.h", "duct", _abi.EXPORTED_DUCT)):
         names = declared_functions(header, prefix)
         assert sorted(listed) == names
         for name in names:
