@@ -372,8 +372,10 @@ def run_duct(args):
             "e2e": {"value": sel / (ms * 1e-3), "unit": "selections/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "trees live on the device; a select has no host input"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                         "kernel": "duct::select_kernel", "bytes_per_selection": bytes_per_sel},
+                         "frac": achieved / pk["hbm_gbs"],
+                         "traffic": sel * 10584.0 if (A, D, Wp) == (8, 16, 8) else None,
+                         "traffic_unit": "bytes per launch, scaled by traversals from an ncu capture of 1024 trees (10.6 KB each)",
+                         "peak_source": pk["source"], "kernel": "duct::select_kernel", "bytes_per_selection": bytes_per_sel},
             "cpu_baseline": cpu, "gpu_launches": 2 * (args.steps + args.warmup), "clocks": clocks}
     print(json.dumps(line))
 
