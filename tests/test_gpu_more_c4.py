@@ -246,3 +246,20 @@ def test_queued_batch_matches_oracle(variant):
     few = ai.run_batch(boards[:8], fills[:8], turns[:8], steps=steps, reseed=True)
     for name in ("best_action", "best_n", "best_n_wins", "actions_ns", "actions_ns_wins"):
         assert np.array_equal(out[name][:8], few[name]), name
+
+
+@pytest.mark.parametrize("variant,n_trees,n_playouts,roots,threads", [
+    ("acp_prodigal", 4, 256, 128, 384),     # many trees, 1792 games a step: a quarter of the games, capped
+    ("ocp_prodigal", 8, 32, 64, 32),        # many trees, 32 games a step: one warp
+    ("ocp_prodigal", 8, 512, 64, 128),
+    ("acp_prodigal", 4, 256, 1, 1024),      # a tree has an SM to itself: one thread per game, capped
+    ("ocp_thrifty", 1, 32, 1, 32),
+])
+def test_block_size_follows_the_games_per_step(variant, n_trees, n_playouts, roots, threads):
+    boards, fills, turns = c4_random_roots(roots, 10, seed=2)
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=8, n_trees=n_trees, n_playouts=n_playouts,
+                variant=variant, verbose_info=False, max_batch=roots)
+    ai.init_device_side_arrays()
+    out = ai.run_batch(boards, fills, turns, steps=8, reseed=True)
+    assert (out["status"] & _abi.STATUS_INTERNAL == 0).all()
+    assert ai.launch_geometry()["threads_per_tree"] == threads
