@@ -290,9 +290,13 @@ class MCTSNC:
         self._adopt_result(res)
         t2 = time.time()
         self.time_total = t2 - t1
+        # the reference builds the two dictionaries only when it prints them (src/mctsnc.py:731-733); they cost nothing
+        # here, so they are always there for a caller like game_runner.py
+        self._make_actions_info()
+        self._make_performance_info()
         if self.verbose_info:
-            print(f"[actions info:\n{_dict_to_str(self._make_actions_info())}]")
-            print(f"[performance info:\n{_dict_to_str(self._make_performance_info())}]")
+            print(f"[actions info:\n{_dict_to_str(self.actions_info)}]")
+            print(f"[performance info:\n{_dict_to_str(self.performance_info)}]")
         best_action_label = str(self.best_action)
         if self.action_index_to_name_function is not None:
             best_action_label += f" ({self.action_index_to_name_function(self.best_action)})"

@@ -28,7 +28,13 @@
  * Parity pin: this file reproduces, field for field, the two tree dumps the
  * reference ships (extras/mctsnc_ocp_thrifty_c4_1000steps.json and
  * extras/mctsnc_acp_thrifty_c4_1000steps.json); tests/test_oracle_golden.py
- * checks that against a digest of those files.
+ * checks that against a digest of those files.  It also replays matches the
+ * reference's authors recorded on their GPU (experiments/[...].zip of the
+ * reference: step count, move, n_root, n, n_wins, playouts, depths and sizes
+ * of every search) search by search, one instance per recorded player with
+ * the random streams running on across searches and games;
+ * tests/test_oracle_experiment_replay.py checks several hundred such searches
+ * of all four variants, draws equal to 1.0f included.
  *
  * Conventions where the reference leaves behaviour undefined:
  *  - numba's uniform_float32 can return exactly 1.0f (probability 2^-25 per
