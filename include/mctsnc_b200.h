@@ -164,6 +164,13 @@ int mctsnc_export_rng(mctsnc_handle *h, int32_t search, int32_t which, uint64_t 
 int mctsnc_query(mctsnc_handle *h, int32_t *threads_per_tree, int32_t *blocks_per_sm, int32_t *sm_count,
                  int64_t *bytes_allocated);
 
+/* Diagnostic, no counterpart in the reference: record every slice of the following batched Connect-4 launches that run
+   through the work queue (more trees than blocks fit on the device): 4 int64 per slice -- tree, start and end of the
+   slice in nanoseconds of the device's global timer, (SM id << 32) | steps run.  max_records = 0 switches it off.
+   mctsnc_read_slices copies the records of the last launch to the host (after the launch has been waited for). */
+int mctsnc_trace_slices(mctsnc_handle *h, int32_t max_records);
+int mctsnc_read_slices(mctsnc_handle *h, int64_t *dst, int32_t max_records, int32_t *n_records);
+
 /* One Connect-4 search that allocates nothing (no counterpart in the reference, whose searcher always allocates its
    device arrays in init_device_side_arrays).  For callers that cannot allocate device memory themselves: code running
    while a framework's caching allocator owns the device, services that forbid allocation after start-up, plug-ins that

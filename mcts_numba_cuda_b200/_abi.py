@@ -22,7 +22,7 @@ E_BAD_ARGUMENT, E_UNSUPPORTED, E_NO_MEMORY, E_BAD_ROOT, E_CAPACITY, E_NO_DEVICE 
 # symbols declared in include/mctsnc_b200.h; the CPU test-suite checks that the library exports every one of them
 EXPORTED = ["mctsnc_create", "mctsnc_destroy", "mctsnc_reset_rng", "mctsnc_run", "mctsnc_run_batch",
             "mctsnc_search_batch_device", "mctsnc_finish_batch_device", "mctsnc_export", "mctsnc_export_rng",
-            "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_error_string"]
+            "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_trace_slices", "mctsnc_read_slices", "mctsnc_error_string"]
 # the PUCT entry points keep the names of the reference's native library (include/puct_b200.h)
 EXPORTED_PUCT = ["puct_select_winner_recalc_launch", "puct_select_virtual_loss_launch", "puct_backup_launch",
                  "puct_cpp_cuda_error_string"]
@@ -90,6 +90,8 @@ def lib():
         L.mctsnc_export_rng.argtypes = [vp, i32, i32, vp, i64]
         L.mctsnc_query.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i64)]
         L.mctsnc_search_c4_static.argtypes = [vp, vp, i32, i32, i32, i32, i64, ctypes.c_float, ctypes.c_uint64, vp, vp]
+        L.mctsnc_trace_slices.argtypes = [vp, i32]
+        L.mctsnc_read_slices.argtypes = [vp, vp, i32, ctypes.POINTER(i32)]
         L.mctsnc_error_string.argtypes = [ctypes.c_int]
         L.mctsnc_error_string.restype = ctypes.c_char_p
         for name in EXPORTED[:-1]:

@@ -707,6 +707,17 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
         if (!queued) break;
         __syncthreads();  // every thread's writes of the slice precede the fence of thread 0
         if (tid == 0) {
+            if (p.trace) {
+                const int k = atomicAdd(p.trace_count, 1);
+                if (k < p.trace_cap) {
+                    unsigned sm;
+                    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+                    p.trace[4 * k] = g;
+                    p.trace[4 * k + 1] = t_start;
+                    p.trace[4 * k + 2] = global_timer_ns();
+                    p.trace[4 * k + 3] = ((long long)sm << 32) | (unsigned)n_steps;
+                }
+            }
             const int left = rem - n_steps;
             p.remaining[g] = left;
             __threadfence();

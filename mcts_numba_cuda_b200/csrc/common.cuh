@@ -192,6 +192,11 @@ struct SearchParams {
     int *remaining;          // [trees] steps of this launch a tree still has to do
     int ring_cap;
     int chunk;               // steps per slice
+    // optional record of every slice of a queued launch (nullptr: none): 4 words per slice -- tree, start and end in
+    // nanoseconds of %globaltimer, (SM id << 32) | steps
+    long long *trace;
+    int *trace_count;
+    int trace_cap;
 };
 
 }  // namespace mctsnc

@@ -82,6 +82,9 @@ struct mctsnc_handle {
     WorkQueues *queue = nullptr;          // Connect 4: work queue of batched launches
     QueueCell *ring = nullptr;            // [QUEUE_LEVELS][n_trees_total]
     int *remaining = nullptr;             // [n_trees_total]
+    long long *trace = nullptr;           // optional slice record of queued launches: [trace_cap][4]
+    int *trace_count = nullptr;
+    int trace_cap = 0;
     // Gomoku only
     unsigned *gboard = nullptr;           // [trees][cap][16]
     gomoku::StepInfo *gstep = nullptr;    // [trees]
@@ -486,6 +489,8 @@ void release(mctsnc_handle *h) {
     cudaFree(h->queue);
     cudaFree(h->ring);
     cudaFree(h->remaining);
+    cudaFree(h->trace);
+    cudaFree(h->trace_count);
     cudaFree(h->gboard);
     cudaFree(h->gstep);
     cudaFree(h->path_ns);
@@ -669,6 +674,9 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
     p.remaining = nullptr;
     p.ring_cap = 0;
     p.chunk = 0;
+    p.trace = nullptr;
+    p.trace_count = nullptr;
+    p.trace_cap = 0;
     if (trees > resident && steps > SLICE_STEPS) {
         init_queue_kernel<<<(unsigned)((trees + 255) / 256), 256, 0, stream>>>(h->queue, h->ring, h->remaining, (int)trees, steps);
         p.queue = h->queue;
@@ -676,6 +684,12 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
         p.remaining = h->remaining;
         p.ring_cap = (int)trees;
         p.chunk = SLICE_STEPS;
+        if (h->trace) {
+            cudaMemsetAsync(h->trace_count, 0, sizeof(int), stream);
+            p.trace = h->trace;
+            p.trace_count = h->trace_count;
+            p.trace_cap = h->trace_cap;
+        }
         grid = (unsigned)resident;
     }
     if (is_ocp(h->cfg)) c4::search_kernel<true><<<grid, threads, h->dyn_smem, stream>>>(p);
@@ -1185,6 +1199,35 @@ extern "C" int mctsnc_query(mctsnc_handle *h, int32_t *threads_per_tree, int32_t
     return 0;
 }
 
+extern "C" int mctsnc_trace_slices(mctsnc_handle *h, int32_t max_records) {
+    if (!h || max_records < 0) return MCTSNC_E_BAD_ARGUMENT;
+    cudaFree(h->trace);
+    cudaFree(h->trace_count);
+    h->trace = nullptr;
+    h->trace_count = nullptr;
+    h->trace_cap = 0;
+    if (max_records == 0) return 0;
+    int rc = dev_alloc(h, &h->trace, 4LL * max_records);
+    if (!rc) rc = dev_alloc(h, &h->trace_count, 1);
+    if (rc) return rc;
+    CUDA_TRY(cudaMemset(h->trace_count, 0, sizeof(int)));
+    h->trace_cap = max_records;
+    return 0;
+}
+
+extern "C" int mctsnc_read_slices(mctsnc_handle *h, int64_t *dst, int32_t max_records, int32_t *n_records) {
+    if (!h || !n_records || (max_records > 0 && !dst)) return MCTSNC_E_BAD_ARGUMENT;
+    *n_records = 0;
+    if (!h->trace) return 0;
+    int n = 0;
+    CUDA_TRY(cudaMemcpy(&n, h->trace_count, sizeof(int), cudaMemcpyDeviceToHost));
+    if (n > h->trace_cap) n = h->trace_cap;
+    if (n > max_records) n = max_records;
+    if (n > 0) CUDA_TRY(cudaMemcpy(dst, h->trace, sizeof(long long) * 4 * n, cudaMemcpyDeviceToHost));
+    *n_records = n;
+    return 0;
+}
+
 extern "C" const char *mctsnc_error_string(int code) {
     switch (code) {
     case 0: return "success";
@@ -1358,6 +1401,9 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
     p.remaining = nullptr;
     p.ring_cap = 0;
     p.chunk = 0;
+    p.trace = nullptr;
+    p.trace_count = nullptr;
+    p.trace_cap = 0;
     const size_t dyn_smem = sizeof(ulonglong2) * (size_t)per_tree;   // <= 28 KB: below the 48 KB that need an opt-in
     if (ocp) c4::search_kernel<true><<<n_trees, 256, dyn_smem, s>>>(p);
     else c4::search_kernel<false><<<n_trees, 256, dyn_smem, s>>>(p);

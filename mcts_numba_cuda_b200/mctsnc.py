@@ -427,6 +427,23 @@ class MCTSNC:
         return {"threads_per_tree": thr.value, "blocks_per_sm": per_sm.value, "sm_count": sms.value,
                 "device_bytes": nbytes.value}
 
+    def trace_slices(self, max_records):
+        """Diagnostic: record every slice of the following batched launches that go through the work queue
+        (``max_records`` = 0 switches it off); see ``read_slices``."""
+        if self._handle is None:
+            raise RuntimeError("[MCTSNC: init_device_side_arrays() has to be called first]")
+        _abi.check(_abi.lib().mctsnc_trace_slices(self._handle, int(max_records)))
+        self._trace_cap = int(max_records)
+
+    def read_slices(self):
+        """Slices of the last batched launch as int64[n, 4]: tree, start ns, end ns (device global timer),
+        (SM id << 32) | steps."""
+        cap = getattr(self, "_trace_cap", 0)
+        out = np.zeros((max(cap, 1), 4), dtype=np.int64)
+        n = ctypes.c_int32(0)
+        _abi.check(_abi.lib().mctsnc_read_slices(self._handle, out.ctypes.data, cap, ctypes.byref(n)))
+        return out[:n.value]
+
     def export(self, name, search=0, max_nodes=None):
         """Device arrays of the last run in the reference's formats (what ``_json_dump`` copies to the host)."""
         fid, dtype = self._EXPORT[name]

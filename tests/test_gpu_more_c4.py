@@ -263,3 +263,27 @@ def test_block_size_follows_the_games_per_step(variant, n_trees, n_playouts, roo
     out = ai.run_batch(boards, fills, turns, steps=8, reseed=True)
     assert (out["status"] & _abi.STATUS_INTERNAL == 0).all()
     assert ai.launch_geometry()["threads_per_tree"] == threads
+
+
+def test_slice_trace_accounts_for_every_step_of_every_tree():
+    """The diagnostic record of a queued launch: every tree gets its steps in slices of at most 32, one after the other."""
+    B, T, steps = 150, 4, 100
+    boards, fills, turns = c4_random_roots(B, 20, seed=9)
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=T, n_playouts=64, variant="acp_prodigal",
+                verbose_info=False, max_batch=B, threads_per_tree=384)
+    ai.init_device_side_arrays()
+    ai.trace_slices(B * T * 4 + 8)
+    plain = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    rec = ai.read_slices()
+    assert len(rec) == B * T * 4                      # 32 + 32 + 32 + 4 steps
+    tree, t0, t1, steps_run = rec[:, 0], rec[:, 1], rec[:, 2], rec[:, 3] & 0xFFFFFFFF
+    assert (t1 >= t0).all() and set(np.unique(steps_run)) == {4, 32}
+    order = np.lexsort((t0, tree))
+    tree, t0, t1, steps_run = tree[order].reshape(B * T, 4), t0[order].reshape(B * T, 4), t1[order].reshape(B * T, 4), steps_run[order].reshape(B * T, 4)
+    assert (tree == np.arange(B * T)[:, None]).all() and (steps_run.sum(axis=1) == steps).all()
+    assert (t0[:, 1:] >= t1[:, :-1]).all()            # a tree's slices never overlap
+    ai.trace_slices(0)
+    again = ai.run_batch(boards, fills, turns, steps=steps, reseed=True)
+    assert len(ai.read_slices()) == 0
+    for name in ("best_action", "best_n", "best_n_wins", "actions_ns"):
+        assert np.array_equal(plain[name], again[name]), name
