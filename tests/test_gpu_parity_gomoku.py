@@ -108,3 +108,30 @@ def test_gomoku_batch_equals_single_runs():
         orc.run(boards[b], None, int(turns[b]), steps)
         compare(ai, orc, search=b)
         assert out["best_action"][b] == orc.best_action and out["playouts"][b] == orc.playouts
+
+
+def test_gomoku_overlines_are_not_wins_in_playouts():
+    """Rows of six stones on the board (they cannot arise by play, but the search does not mind): a stone added at either
+    end makes a row of seven, which the reference does not count as a win (it looks at most five stones either way and
+    wants exactly four, ``src/mctsnc_game_mechanics.py:220-272``).  The playouts meet this in all four directions."""
+    board = np.zeros((15, 15), np.int8)
+    board[7, 2:8] = 1                                   # horizontal
+    board[1:7, 12] = 1                                  # vertical
+    for k in range(6):
+        board[8 + k, 2 + k] = 1                         # diagonal, (8,2) .. (13,7)
+        board[13 - k, 9 + k] = 1                        # anti-diagonal, (13,9) .. (8,14)
+    # as many stones of the other side, none of them next to another
+    spots = [(0, c) for c in range(0, 15, 2)] + [(14, c) for c in range(0, 15, 2)] + [(r, 10) for r in range(2, 7, 2)] + \
+            [(3, c) for c in range(0, 10, 2)]
+    for r, c in spots[:int((board == 1).sum())]:
+        assert board[r, c] == 0
+        board[r, c] = -1
+    assert (board == 1).sum() == (board == -1).sum() == 24
+    steps = 5
+    for seed, turn in ((0, 1), (1, -1)):
+        ai, orc = make_pair("acp_prodigal", 1, 64, steps, seed=seed)
+        best = ai.run(board, None, turn)
+        orc.run(board, None, turn, steps)
+        compare(ai, orc)
+        assert int(best) == orc.best_action and ai._res["plies"] == orc.plies
+        assert (ai.best_win_flag, int(ai.best_n), int(ai.best_n_wins)) == (orc.best_win_flag, orc.best_n, orc.best_n_wins)
