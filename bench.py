@@ -503,10 +503,10 @@ def main():
         "issue_roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12,
                            "unit": "T thread-inst/s", "frac": inst_achieved / peak_inst,
                            "binding_unit": ("integer/logic pipe (16 lanes per clock and scheduler): 87.8 % of its peak, 71.5 % of "
-                                            "issue slots, 21.9 of 32 lanes active (ncu, profiles/c4_acp_search_kernel_256roots_200steps.md)"
+                                            "issue slots, 21.9 of 32 lanes active (ncu capture of the 256-root, 200-step case)"
                                             if args.game == "c4" else
                                             "integer/logic pipe: 76.4 % of its peak, 72.0 % of issue slots, 21.2 of 32 lanes active "
-                                            "(ncu, profiles/gomoku_playout_kernel_T4_P256.md)"),
+                                            "(ncu capture of one step of a 4 x 256 search)"),
                            "plies_per_playout": plies_per_launch / max(playouts_per_launch, 1),
                            "inst_per_ply_yardstick": G["inst_per_ply"], "sm_count": sm_count,
                            "peak_clock_mhz": pk["sm_max_mhz"]},
