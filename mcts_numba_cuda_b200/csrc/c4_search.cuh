@@ -724,7 +724,12 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
             if (left > 0) {
                 // band of the time the tree still needs at the pace of this slice, counted down from the longest whole
                 // search seen so far in this launch
-                const float us_per_step = (float)(global_timer_ns() - t_start) * 1e-3f / (float)n_steps;
+                // the pace of a tree changes from slice to slice (its tree deepens, its neighbours on the SM change): half
+                // the weight goes to the slices before (worth 1-2 % on the headline batch: 16.7-17.2 G playouts/s against
+                // 16.6-16.8 with the last slice alone)
+                float us_per_step = (float)(global_timer_ns() - t_start) * 1e-3f / (float)n_steps;
+                if (rem != p.steps) us_per_step = 0.5f * us_per_step + 0.5f * p.state[g].us_per_step;
+                p.state[g].us_per_step = us_per_step;
                 const int whole = (int)fminf(us_per_step * (float)p.steps, 2e9f);
                 const int longest = max(atomicMax(&p.queue->longest_us, whole), max(whole, 1));
                 const float below = QUEUE_LEVELS_PER_OCTAVE * log2f((float)longest / fmaxf(us_per_step * (float)left, 1e-3f));

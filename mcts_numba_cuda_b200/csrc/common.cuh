@@ -59,6 +59,8 @@ struct TreeState {
     unsigned status;
     unsigned long long plies;
     unsigned long long ub_draws;
+    float us_per_step;   // work queue: smoothed time per step of the tree's slices in the current launch (microseconds)
+    int reserved;
 };
 
 // Work queue of a batched launch.  A tree's search is cut into slices of `chunk` steps; the blocks of a persistent grid
