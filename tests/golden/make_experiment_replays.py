@@ -23,6 +23,10 @@ SELECTED = [
     "mcts_5_inf_vanilla;mctsnc_1_inf_2_64_ocp_thrifty", "mcts_5_inf_vanilla;mctsnc_1_inf_4_128_acp_thrifty",
     "mcts_5_inf_vanilla;mctsnc_1_inf_8_256_ocp_prodigal", "mcts_5_inf_vanilla;mctsnc_1_inf_4_256_acp_prodigal",
     "mcts_5_inf_vanilla;mctsnc_5_inf_4_256_acp_prodigal", "mctsnc_5_inf_4_256_acp_thrifty;mctsnc_5_inf_4_256_acp_prodigal",
+    "mcts_5_inf_vanilla;mctsnc_1_inf_8_256_acp_thrifty", "mcts_5_inf_vanilla;mctsnc_1_inf_8_32_acp_prodigal",
+    "mcts_5_inf_vanilla;mctsnc_1_inf_2_256_ocp_prodigal", "mcts_5_inf_vanilla;mctsnc_1_inf_4_64_ocp_thrifty",
+    "mcts_5_inf_vanilla;mctsnc_1_inf_1_256_acp_thrifty", "mcts_5_inf_vanilla;mctsnc_1_inf_8_128_ocp_thrifty",
+    "mcts_5_inf_vanilla;mctsnc_1_inf_2_128_acp_prodigal", "mctsnc_5_inf_4_128_ocp_thrifty;mctsnc_5_inf_4_256_ocp_prodigal",
 ]
 INSTANCE = re.compile(r"MCTSNC\(search_time_limit=([\d.]+), search_steps_limit=(\w+), n_trees=(\d+), n_playouts=(\d+), "
                       r"variant='(\w+)', device_memory=([\d.]+), ucb_c=([\d.]+), seed: (\d+)\)")

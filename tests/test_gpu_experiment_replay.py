@@ -53,6 +53,15 @@ def replay(key, side, limit):
     ("mcts_5_inf_vanilla;mctsnc_5_inf_4_256_acp_prodigal", "ai_b", 66),
     ("mctsnc_5_inf_4_256_acp_thrifty;mctsnc_5_inf_4_256_acp_prodigal", "ai_a", 72),
     ("mctsnc_5_inf_4_256_acp_thrifty;mctsnc_5_inf_4_256_acp_prodigal", "ai_b", 36),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_8_256_acp_thrifty", "ai_b", 79),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_8_32_acp_prodigal", "ai_b", 97),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_2_256_ocp_prodigal", "ai_b", 90),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_4_64_ocp_thrifty", "ai_b", 79),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_1_256_acp_thrifty", "ai_b", 96),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_8_128_ocp_thrifty", "ai_b", 71),
+    ("mcts_5_inf_vanilla;mctsnc_1_inf_2_128_acp_prodigal", "ai_b", 88),
+    ("mctsnc_5_inf_4_128_ocp_thrifty;mctsnc_5_inf_4_256_ocp_prodigal", "ai_a", 105),
+    ("mctsnc_5_inf_4_128_ocp_thrifty;mctsnc_5_inf_4_256_ocp_prodigal", "ai_b", 107),
 ])
 def test_recorded_matches_are_reproduced(key, side, limit):
     assert replay(key, side, limit) == limit
