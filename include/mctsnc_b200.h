@@ -127,7 +127,9 @@ int mctsnc_run_batch(mctsnc_handle *h, int32_t batch, const int8_t *boards, cons
    DEVICE buffer partial_sums; after the caller has summed those buffers over the handles of a search (all-reduce),
    finish runs the argmax of _reduce_over_actions_* (src/mctsnc.py:2299-2375) on the summed values and fills results.
    stream: a cudaStream_t (NULL = default stream).  search is asynchronous.  boards_host == NULL searches the roots of
-   the previous call again (they stay resident on the device).  finish synchronises and copies the results to the
+   the previous call again (they stay resident on the device).  One search per handle may be in flight: a call that
+   stages new roots first waits until the previous call's copies have read the (single) pinned staging buffer, and the
+   timing events behind device_ms are those of the last search call.  finish synchronises and copies the results to the
    host, unless results == NULL: then it only launches the argmax kernel and returns. */
 int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards_host, const int8_t *extra_infos_host,
                                const int8_t *turns_host, int64_t steps, int32_t reseed, int64_t *partial_sums_device,
@@ -175,14 +177,18 @@ int mctsnc_read_slices(mctsnc_handle *h, int64_t *dst, int32_t max_records, int3
    device arrays in init_device_side_arrays).  For callers that cannot allocate device memory themselves: code running
    while a framework's caching allocator owns the device, services that forbid allocation after start-up, plug-ins that
    are handed a stream and buffers only.  Tree pools, random streams and bookkeeping live in one fixed array inside the
-   library image (about 1.6 MB on every device that loads the library), hence the limits below; beyond them the call
+   library image (about 0.75 MB on every device that loads the library), hence the limits below; beyond them the call
    returns MCTSNC_E_CAPACITY.
    board/extra_info/turn: host, as for mctsnc_run.  out_device: DEVICE buffer of 3*7+4 int64 supplied by the caller:
    root_ns[7], actions_ns[7], actions_ns_wins[7] (indexed by action), then best_action, best_win_flag, best_n, best_n_wins.
    The result equals mctsnc_run on a freshly created handle with the same arguments.  Work is queued on `stream` and
    not waited for, except that the first call on a device, and any call with a new (seed, n_trees, n_playouts, variant),
-   prepares the seeded streams and synchronises: make such a call before capturing the stream.  All calls share the
-   one array: it is re-initialised at the start of every call, and calls whose GPU work overlaps race on it. */
+   looks up the array's device address, prepares the seeded streams and synchronises: such a call has to come before
+   any stream capture (nothing is said here about capturing the later ones).  The root is passed to the device as
+   kernel arguments; no host memory of the caller is read after the call returns.  All calls share the one array: it
+   is re-initialised at the start of every call, and calls whose GPU work overlaps (other streams, other host threads)
+   race on it.  The host-side set-up (address look-up, stream cache) is serialised by a mutex inside the library, so
+   threads driving different devices may call concurrently; each device has its own copy of the array. */
 #define MCTSNC_STATIC_MAX_TREES 4
 #define MCTSNC_STATIC_MAX_PLAYOUTS 256
 #define MCTSNC_STATIC_MAX_STEPS 512

@@ -7,6 +7,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <mutex>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -104,6 +105,8 @@ struct mctsnc_handle {
     unsigned char *h_flags = nullptr;
     DevResult *h_dres = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev_staged = nullptr;  // recorded behind the host-to-device copies of the staged roots
+    bool staging_in_flight = false;
     float last_ms = 0.f;
     long long last_steps = 0;
     int staged_roots = 0;  // roots resident on the device from the last staging
@@ -510,6 +513,7 @@ void release(mctsnc_handle *h) {
     cudaFreeHost(h->h_dres);
     if (h->ev0) cudaEventDestroy(h->ev0);
     if (h->ev1) cudaEventDestroy(h->ev1);
+    if (h->ev_staged) cudaEventDestroy(h->ev_staged);
 }
 
 #ifndef MCTSNC_SLICE_STEPS
@@ -559,6 +563,12 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
                 cudaStream_t stream) {
     const int cells = h->cfg.board_rows * h->cfg.board_cols;
     const int extra = h->cfg.extra_info_memory;
+    // the pinned staging buffers are about to be rewritten: the copies of the previous call (asynchronous entry points
+    // return before they ran) must have read them
+    if (h->staging_in_flight) {
+        CUDA_TRY(cudaEventSynchronize(h->ev_staged));
+        h->staging_in_flight = false;
+    }
     if (is_gomoku(h->cfg)) {
         for (int b = 0; b < batch; b++) {
             if (turns[b] != 1 && turns[b] != -1) return MCTSNC_E_BAD_ARGUMENT;
@@ -568,6 +578,8 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
         }
         CUDA_TRY(cudaMemcpyAsync(h->root_gboard, h->h_root_gboard, sizeof(unsigned) * 16 * batch, cudaMemcpyHostToDevice, stream));
         CUDA_TRY(cudaMemcpyAsync(h->root_turn, h->h_root_turn, batch, cudaMemcpyHostToDevice, stream));
+        CUDA_TRY(cudaEventRecord(h->ev_staged, stream));
+        h->staging_in_flight = true;
         return 0;
     }
     for (int b = 0; b < batch; b++) {
@@ -579,6 +591,8 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
     }
     CUDA_TRY(cudaMemcpyAsync(h->root_board, h->h_root_board, sizeof(ulonglong2) * batch, cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaMemcpyAsync(h->root_turn, h->h_root_turn, batch, cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaEventRecord(h->ev_staged, stream));
+    h->staging_in_flight = true;
     return 0;
 }
 
@@ -853,6 +867,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc && cudaMallocHost((void **)&h->h_dres, sizeof(DevResult) * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && cudaEventCreate(&h->ev0) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && cudaEventCreate(&h->ev1) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaEventCreateWithFlags(&h->ev_staged, cudaEventDisableTiming) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc) rc = (int)cudaMemset(h->state, 0, sizeof(TreeState) * h->n_trees_total);
     if (!rc) rc = (int)cudaMemset(h->actions_expanded, 0, sizeof(short) * h->n_trees_total * (h->A + 2));
     if (!rc) rc = (int)cudaMemset(h->child_out, 0, sizeof(int) * h->n_trees_total * h->A * 2);
@@ -1255,10 +1270,11 @@ extern "C" const char *mctsnc_error_string(int code) {
 //
 // The array's name is only a host-side stand-in for the device object, not a device address: the first call on a device
 // (with that device current) asks the runtime for the address with cudaGetSymbolAddress and every launch gets that
-// pointer.  That first call also fills the cache of seeded streams; it synchronises, so make it before capturing a
-// stream.  All calls share the one array and it keeps what the last call left: what has to start from zero is
+// pointer.  That first call also fills the cache of seeded streams; it synchronises, so it has to come before any
+// stream capture.  All calls share the one array and it keeps what the last call left: what has to start from zero is
 // cleared on the caller's stream at the start of every call, and two calls whose work overlaps on the GPU (different
-// streams, different host threads) would race on it -- run them one after the other.
+// streams, different host threads) would race on it -- run them one after the other.  The host-side statics (address
+// per device, stream cache, staging buffer) are guarded by a mutex.
 namespace {
 namespace fixed {
 
@@ -1289,6 +1305,9 @@ struct Scratch {
     signed char root_turn[16];
 };
 
+// the figure quoted in include/mctsnc_b200.h ("about 0.75 MB")
+static_assert(sizeof(Scratch) > 700 * 1024 && sizeof(Scratch) < 800 * 1024, "update the size quoted in the header");
+
 static __device__ __align__(256) unsigned char g_static_scratch[sizeof(Scratch)];
 
 struct DeviceSetup {
@@ -1299,6 +1318,15 @@ struct DeviceSetup {
 };
 DeviceSetup g_setup[MAX_DEVICES];
 ulonglong2 g_host_streams[MAX_STREAMS];   // staging for the seeded streams (static: no host allocation either)
+std::mutex g_setup_mutex;                 // the two objects above are shared by all devices and all host threads
+
+// the root arrives as kernel arguments (by value): no host memory is read after the call has returned
+__global__ void set_root_kernel(ulonglong2 *root_board, signed char *root_turn, ulonglong2 root, int turn) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        root_board[0] = root;
+        root_turn[0] = (signed char)turn;
+    }
+}
 
 __global__ void copy_streams_kernel(ulonglong2 *dst, const ulonglong2 *src, int n) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
@@ -1329,6 +1357,11 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
     CUDA_TRY(cudaGetDevice(&device));
     if (device < 0 || device >= MAX_DEVICES) return MCTSNC_E_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    ulonglong2 root;
+    int rc = c4_encode_root(board, extra_info, &root);
+    if (rc) return rc;
+    // the set-up below touches host-side state shared by every device and thread: one caller at a time
+    std::unique_lock<std::mutex> setup_lock(g_setup_mutex);
     DeviceSetup &su = g_setup[device];
     if (!su.ptr) {
         // once per device, with that device current: the device address behind the symbol
@@ -1338,9 +1371,6 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
         su.streams_cached = false;
     }
     Scratch *sc = su.ptr;
-    ulonglong2 root;
-    int rc = c4_encode_root(board, extra_info, &root);
-    if (rc) return rc;
     const bool ocp = variant == MCTSNC_OCP_THRIFTY || variant == MCTSNC_OCP_PRODIGAL;
     const int per_tree = ocp ? n_playouts : A * n_playouts;
     const int n_streams = n_trees * per_tree;
@@ -1364,13 +1394,12 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
         su.ocp = (int)ocp;
         su.streams_cached = true;
     }
-    // what has to start from zero, and the root (17 bytes from the stack: staged by the runtime before it returns)
+    setup_lock.unlock();
+    // what has to start from zero, and the root
     CUDA_TRY(cudaMemsetAsync(sc->state, 0, sizeof(sc->state), s));
     CUDA_TRY(cudaMemsetAsync(sc->child_out, 0, sizeof(sc->child_out), s));
     CUDA_TRY(cudaMemsetAsync(sc->actions_expanded, 0, sizeof(sc->actions_expanded), s));
-    const signed char t8 = (signed char)turn;
-    CUDA_TRY(cudaMemcpyAsync(sc->root_board, &root, sizeof(root), cudaMemcpyHostToDevice, s));
-    CUDA_TRY(cudaMemcpyAsync(sc->root_turn, &t8, 1, cudaMemcpyHostToDevice, s));
+    set_root_kernel<<<1, 32, 0, s>>>(sc->root_board, sc->root_turn, root, turn);
     copy_streams_kernel<<<32, 256, 0, s>>>(sc->rng, sc->rng_base, n_streams);
     if (ocp) copy_streams_kernel<<<1, 32, 0, s>>>(sc->rng_expand, sc->rng_expand_base, n_trees);
     SearchParams p;

@@ -67,17 +67,23 @@ class RootParallelMCTSNC:
         self.local.init_device_side_arrays()
         self.max_batch = max_batch
         self._sums = None
+        self._batch = 0   # roots staged by the last call that brought boards (0: none yet; the library then refuses boards=None)
 
     def search_async(self, boards, extras, turns, steps, reseed=True, stream=None):
-        """Launches the searches and the all-reduce on the current CUDA stream; nothing is copied back."""
+        """Launches the searches, the all-reduce and the final argmax on one CUDA stream (torch's current stream, or the
+        ``cudaStream_t`` handle given as ``stream``); nothing is copied back."""
         import torch
+        if stream is not None and stream != torch.cuda.current_stream().cuda_stream:
+            # the all-reduce is ordered against torch's current stream: make the given stream that one
+            with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
+                return self.search_async(boards, extras, turns, steps, reseed)
         import torch.distributed as dist
         ai = self.local
         A = ai.state_max_actions
-        batch = self._batch if boards is None else len(boards)
+        batch = max(self._batch, 1) if boards is None else len(boards)
         if self._sums is None:
             self._sums = torch.empty((self.max_batch, 3 * A), dtype=torch.int64, device=f"cuda:{ai.device}")
-        cu_stream = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        cu_stream = torch.cuda.current_stream().cuda_stream
         if boards is not None:
             boards = np.ascontiguousarray(boards, dtype=np.int8)
             extras = np.ascontiguousarray(extras, dtype=np.int8) if extras is not None else None
