@@ -9,8 +9,13 @@ MCTS steps).  With N > 1 (launched by torchrun, one rank per GPU) every rank gro
 random streams of a 4N-tree search, and the per-root-action sums are all-reduced over NCCL once per pass (root
 parallelism; per-GPU work is fixed: weak scaling).  Rank 0 prints one JSON line.
 
-`--impl reference` times the CPU restatement of the reference's kernels (oracle/) on the host cores, one root per
-thread, on a bounded sample of the same workload.
+`--impl reference` times the CPU restatement of the reference's kernels (oracle/) on all host cores, one tree per
+thread, on a bounded sample of the same workload (same search: 4 trees x 256 playouts x 2000 steps per root; fewer roots).
+
+After the headline's timed regions a single-GPU run appends `secondary`: short device-timed runs of the other
+configurations (Connect 4 ocp_thrifty 1 x 32, Gomoku acp_prodigal 4 x 256, the PUCT and DUCT selects) and, where a copy of
+the reference lies under baseline/_ref (python baseline/install_reference.py), the reference itself on this machine:
+its CPU search `MCTS` on the host cores and its numba.cuda `MCTSNC` on this GPU.
 """
 import argparse
 import json
@@ -32,9 +37,32 @@ GAMES = {"c4": {"shape": (6, 7), "extra": 7, "actions": 7, "inst_per_ply": 65.0,
 # move pick and placement ~18, line test through the new stone 16 (Connect 4) / ~55 (Gomoku), draw test and loop ~6.
 # It is the yardstick of the issue roofline, not a count of the compiled code.
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one search-kernel launch, from a one-pass ncu capture of the default
-# workload; key: game, variant, trees, playouts, search steps, roots
-MEASURED_TRAFFIC_BYTES = {("c4", "acp_prodigal", 4, 256, 2000, 256): 133639424 + 409819136}
+KERNEL_SOURCES = {"c4": ("c4_search.cuh", "common.cuh", "rng.cuh"), "gomoku": ("gomoku_search.cuh", "common.cuh", "rng.cuh")}
+
+
+def kernel_source_sha(game):
+    """Identifies the kernel a profile was taken on: hash of the sources the search kernel of `game` is compiled from."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES[game]:
+        with open(os.path.join(ROOT, "mcts_numba_cuda_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def profiler_readings(game, workload_key):
+    """Figures read off ncu captures (profiles/search_kernel_ncu.json: DRAM traffic per launch, pipe and issue
+    utilisation, lanes per instruction).  They describe the kernel they were captured on: when the kernel sources have
+    changed since, or the workload is another one, the answer is None and the bench line carries nulls."""
+    path = os.path.join(ROOT, "profiles", "search_kernel_ncu.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        entries = json.load(f)
+    for e in entries:
+        if e.get("game") == game and e.get("kernel_source_sha") == kernel_source_sha(game) and e.get("workload_key") == workload_key:
+            return e
+    return None
 
 
 def parse_args():
@@ -60,7 +88,9 @@ def parse_args():
     ap.add_argument("--max-plies", type=int, default=20)
     ap.add_argument("--threads-per-tree", type=int, default=0)
     ap.add_argument("--cpu-sample-roots", type=int, default=0, help="roots of the CPU baseline sample (0 = choose)")
-    ap.add_argument("--cpu-sample-steps", type=int, default=400)
+    ap.add_argument("--cpu-sample-steps", type=int, default=0, help="search steps of the CPU legs (0 = reference arm: the workload's; cpu_baseline leg: 400)")
+    ap.add_argument("--internal", default="", help=argparse.SUPPRESS)
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations and the reference's own runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -129,62 +159,165 @@ def make_roots(args):
     return c4_random_roots(args.roots, args.max_plies, seed=0)
 
 
-def oracle_search(job):
+def oracle_tree_search(job):
+    """One tree of one root's search with the oracle: tree `tree` of a search with `trees` trees (its random streams are
+    those of that tree in the whole search, so the trees of a root together are exactly the root's search)."""
     from oracle.oracle import OracleMCTSNC
-    board, fills, turn, trees, playouts, variant, steps, game = job
+    board, fills, turn, trees, tree, playouts, variant, steps, game = job
     G = GAMES[game]
-    o = OracleMCTSNC(G["shape"], G["extra"], G["actions"], n_trees=trees, n_playouts=playouts, variant=variant, seed=0,
-                     device_memory=16.0 if game == "gomoku" else 2.0, node_capacity=steps * G["actions"] + G["actions"] + 8)
-    t0 = time.perf_counter()
+    o = OracleMCTSNC(G["shape"], G["extra"], G["actions"], n_trees=1, n_playouts=playouts, variant=variant, seed=0,
+                     device_memory=16.0 if game == "gomoku" else 2.0, node_capacity=steps * G["actions"] + G["actions"] + 8,
+                     tree_offset=tree, n_trees_global=trees)
     o.run(board, fills, int(turn), steps)
-    return o.playouts, o.plies, time.perf_counter() - t0
+    return o.playouts, o.plies
 
 
 def cpu_port_baseline(args, boards, fills, turns, threads, n_roots, steps):
-    """The oracle (CPU restatement of the reference's kernels) on `threads` host threads, one root per thread."""
+    """The oracle (CPU restatement of the reference's kernels) on `threads` host threads, one tree of one root per
+    thread at a time (the ctypes calls release the interpreter lock).  Returns (playouts, plies, seconds)."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import oracle as om
     om.lib()
     jobs = [(boards[i % len(boards)], fills[i % len(boards)] if fills is not None else None, turns[i % len(boards)],
-             args.trees, args.playouts, args.variant, steps, args.game) for i in range(n_roots)]
+             args.trees, t, args.playouts, args.variant, steps, args.game) for i in range(n_roots) for t in range(args.trees)]
     t0 = time.perf_counter()
     with ThreadPoolExecutor(max_workers=threads) as ex:
-        res = list(ex.map(oracle_search, jobs))
+        res = list(ex.map(oracle_tree_search, jobs))
     wall = time.perf_counter() - t0
-    playouts = sum(r[0] for r in res)
-    plies = sum(r[1] for r in res)
-    return playouts, plies, wall
+    return sum(r[0] for r in res), sum(r[1] for r in res), wall
 
 
-def config_dict(args, n_gpus):
+def config_dict(args, n_gpus, roots=None):
+    roots = args.roots if roots is None else roots
     return {"workload": f"{GAMES[args.game]['name']} {args.variant}, n_trees={args.trees} per GPU, n_playouts={args.playouts}, "
-                        f"search_steps={args.search_steps}, {args.roots} seeded random roots (0..{args.max_plies} plies) per pass",
+                        f"search_steps={args.search_steps}, {roots} seeded random roots (0..{args.max_plies} plies) per pass",
             "trees_per_search_total": args.trees * n_gpus, "parallelism": f"root-parallel x{n_gpus}" if n_gpus > 1 else "single GPU",
             "l2": "no flush: the tree pools of one pass (~0.5 GB) exceed the 126 MB L2", "seed": 0, "ucb_c": 2.0}
 
 
 def run_reference(args, rank):
+    """The reference arm: the CPU restatement of the reference's kernels on every host core.  A pass searches as many of
+    the benchmark's roots as keep all cores busy with one tree each (cores / trees roots), with the full step count."""
     if rank != 0:
         return
     boards, fills, turns = make_roots(args)
     cores = os.cpu_count() or 1
-    steps = args.cpu_sample_steps
-    n_roots = args.cpu_sample_roots or cores
+    steps = args.cpu_sample_steps or args.search_steps
+    n_roots = args.cpu_sample_roots or max(1, cores // args.trees)
     times, total_playouts = [], 0
     for i in range(args.warmup + args.steps):
-        playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, cores, n_roots, steps)
+        # warm-up passes only have to touch the code and the allocator: a tenth of the steps
+        playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, cores, n_roots, steps if i >= args.warmup else max(steps // 10, 1))
         if i >= args.warmup:
             times.append(wall)
             total_playouts += playouts
     value = total_playouts / sum(times)
-    sample = f"{n_roots} roots x {steps} search steps per pass, one root per thread"
+    sample = (f"{n_roots} of the {args.roots} roots x {steps} search steps per pass (the same search per root as the GPU arm), "
+              f"one tree per thread on {cores} threads; warm-up passes run a tenth of the steps")
+    cfg = config_dict(args, args.gpus, roots=n_roots)
+    cfg["search_steps"] = steps
     print(json.dumps({"impl": "reference", "metric": "playouts/sec", "value": value, "unit": "playouts/s", "n_gpus": args.gpus,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
                       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
-                      "data": "synthetic", "config": config_dict(args, args.gpus),
+                      "data": "synthetic", "config": cfg,
                       "cpu_baseline": {"value": value, "unit": "playouts/s", "cores": cores, "kind": "port", "sample": sample},
                       "e2e": {"value": value, "unit": "playouts/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                       "gpu_launches": 0}))
+
+
+REF_SRC = os.path.join(ROOT, "baseline", "_ref", "src")
+
+
+def _reference_state(board, fills, turn):
+    """A state object of the reference's own class ``C4`` (``src/c4.py``) holding the given position."""
+    from c4 import C4
+    s = C4()
+    s.board[:] = board
+    s.column_fills[:] = fills
+    s.turn = int(turn)
+    return s
+
+
+def _reference_mcts_one(job):
+    """One search of the reference's CPU class ``MCTS`` (``src/mcts.py:482-588``; one playout per step)."""
+    import contextlib
+    import io
+    board, fills, turn, steps = job
+    if REF_SRC not in sys.path:
+        sys.path.insert(0, REF_SRC)
+    from mcts import MCTS
+    ai = MCTS(search_time_limit=np.inf, search_steps_limit=steps, vanilla=True, verbose_info=False)
+    root = _reference_state(board, fills, turn)
+    t0 = time.perf_counter()
+    with contextlib.redirect_stdout(io.StringIO()):
+        ai.run(root)
+    return ai.steps, time.perf_counter() - t0
+
+
+def internal_reference_mcts(args):
+    """Child process: the reference's ``MCTS`` on one core, then one search per core on all cores at once."""
+    import multiprocessing as mp
+    boards, fills, turns = make_roots(args)
+    steps = args.search_steps
+    _reference_mcts_one((boards[0], fills[0], turns[0], 200))               # numba compiles the outcome function on first use
+    one = [_reference_mcts_one((boards[i], fills[i], turns[i], steps)) for i in range(3)]
+    cores = os.cpu_count() or 1
+    jobs = [(boards[i % len(boards)], fills[i % len(boards)], turns[i % len(boards)], steps) for i in range(cores)]
+    t0 = time.perf_counter()
+    with mp.get_context("fork").Pool(cores) as pool:
+        pool.map(_reference_mcts_one, jobs[:cores])                           # untimed: every worker compiles
+        t0 = time.perf_counter()
+        res = pool.map(_reference_mcts_one, jobs)
+    wall = time.perf_counter() - t0
+    print(json.dumps({"what": "reference src/mcts.py MCTS(vanilla=True), one playout per step", "search_steps": steps,
+                      "one_core": {"value": sum(r[0] for r in one) / sum(r[1] for r in one), "unit": "playouts/s", "cores": 1,
+                                   "sample": f"3 roots x {steps} steps, sequential"},
+                      "all_cores": {"value": sum(r[0] for r in res) / wall, "unit": "playouts/s", "cores": cores,
+                                    "sample": f"{cores} roots x {steps} steps, one process per core"}}))
+
+
+def internal_reference_numba(args):
+    """Child process: the reference's numba.cuda ``MCTSNC`` (``src/mctsnc.py``), unmodified, on this machine's GPU for the
+    benchmark's configuration; a fresh ``init_device_side_arrays()`` per root, timing as the reference reports it in
+    ``performance_info`` (host clock around its whole ``run``)."""
+    import contextlib
+    import io
+    sys.path.insert(0, REF_SRC)
+    from mctsnc import MCTSNC
+    boards, fills, turns = make_roots(args)
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=float(args.search_steps), n_trees=args.trees,
+                n_playouts=args.playouts, variant=args.variant, device_memory=2.0, ucb_c=2.0, seed=0, verbose_info=True)
+    rows = []
+    with contextlib.redirect_stdout(io.StringIO()):
+        ai.init_device_side_arrays()
+        ai.run(boards[0], fills[0], int(turns[0]))                            # first use
+        for i in range(args.roots):
+            ai.init_device_side_arrays()
+            ai.run(boards[i], fills[i], int(turns[i]))
+            p = ai.performance_info
+            rows.append((int(p["playouts"]), float(p["times_[ms]"]["total"]), int(p["steps"]), int(ai.best_action), int(ai.best_n),
+                         int(ai.best_n_wins)))
+    total_s = sum(r[1] for r in rows) * 1e-3
+    print(json.dumps({"what": "reference src/mctsnc.py MCTSNC (numba.cuda), host-timed per run() as its performance_info does",
+                      "config": str(ai), "value": sum(r[0] for r in rows) / total_s, "unit": "playouts/s",
+                      "steps_per_second": sum(r[2] for r in rows) / total_s, "roots": len(rows),
+                      "best": [[r[3], r[4], r[5]] for r in rows]}))
+
+
+def run_child(mode, args, extra, timeout):
+    """Runs this file again as a child process in one of its internal modes and returns the JSON it prints."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--internal", mode, "--game", args.game, "--variant", args.variant,
+           "--trees", str(args.trees), "--playouts", str(args.playouts), "--search-steps", str(args.search_steps),
+           "--max-plies", str(args.max_plies)] + extra
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"no answer within {timeout} s"}
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    if res.returncode != 0 or not lines:
+        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or [""]
+        return {"unavailable": f"exit code {res.returncode}: {tail[0][:200]}"}
+    return json.loads(lines[-1])
 
 
 def puct_device_case(trees, edges, depth, warps, seed, device):
@@ -282,7 +415,7 @@ def run_puct(args):
                          "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                          "kernel": "puct::select_kernel", "bytes_per_selection": bytes_per_sel},
             "gpu_launches": 2 * (args.steps + args.warmup) * 2, "clocks": clocks}
-    print(json.dumps(line))
+    return line
 
 
 def duct_device_case(trees, actions, depth, warps, seed, device):
@@ -377,16 +510,112 @@ def run_duct(args):
                          "traffic_unit": "bytes per launch, scaled by traversals from an ncu capture of 1024 trees (10.6 KB each)",
                          "peak_source": pk["source"], "kernel": "duct::select_kernel", "bytes_per_selection": bytes_per_sel},
             "cpu_baseline": cpu, "gpu_launches": 2 * (args.steps + args.warmup), "clocks": clocks}
-    print(json.dumps(line))
+    return line
+
+
+def timed_search(game, variant, trees, playouts, steps, roots, max_plies, passes, device):
+    """Device-timed playouts/s of one search configuration: roots resident on the device, streams re-seeded every pass,
+    CUDA events around `passes` passes after one warm-up pass."""
+    import torch
+    from mcts_numba_cuda_b200.distributed import RootParallelMCTSNC
+    from mcts_numba_cuda_b200.roots import c4_random_roots, gomoku_random_roots
+    G = GAMES[game]
+    if game == "gomoku":
+        boards, turns = gomoku_random_roots(roots, max_plies, seed=0)
+        fills = None
+    else:
+        boards, fills, turns = c4_random_roots(roots, max_plies, seed=0)
+    s = RootParallelMCTSNC(G["shape"], G["extra"], G["actions"], n_trees=trees, n_playouts=playouts, variant=variant,
+                           search_steps_limit=steps, max_batch=roots, device=device, rank=0, world_size=1, seed=0, ucb_c=2.0,
+                           device_memory=16.0 if game == "gomoku" else 2.0)
+    s.search_async(boards, fills, turns, steps, reseed=True)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(passes):
+        s.search_async(None, None, None, steps, reseed=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / passes
+    res = s.fetch(roots)
+    playouts_pass, plies_pass = int(res["playouts"].sum()), int(res["plies"].sum())
+    geo = s.local.launch_geometry()
+    peak_inst = geo["sm_count"] * 4 * 32 * peaks()["sm_max_mhz"] * 1e6
+    return {"workload": f"{G['name']} {variant}, n_trees={trees}, n_playouts={playouts}, search_steps={steps}, {roots} roots "
+                        f"(0..{max_plies} plies)", "value": playouts_pass / (ms * 1e-3), "unit": "playouts/s", "ms_per_pass": ms,
+            "passes": passes, "plies_per_playout": plies_pass / max(playouts_pass, 1), "status_bits": int(np.bitwise_or.reduce(res["status"])),
+            "issue_frac": plies_pass * G["inst_per_ply"] / (ms * 1e-3) / peak_inst, "threads_per_tree": geo["threads_per_tree"]}
+
+
+def secondary_runs(args, device):
+    """Short runs of the other configurations, and the reference itself where a copy of it is installed; every entry
+    stands alone (a failure is recorded in its place)."""
+    import copy
+    out = {}
+
+    def attempt(name, fn):
+        try:
+            out[name] = fn()
+        except Exception as e:  # noqa: BLE001 - a secondary figure must not take the headline down
+            out[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    attempt("c4_ocp_thrifty_1x32_200steps_64roots", lambda: timed_search("c4", "ocp_thrifty", 1, 32, 200, 64, 10, 5, device))
+    attempt("gomoku_acp_prodigal_4x256_500steps_1root", lambda: timed_search("gomoku", "acp_prodigal", 4, 256, 500, 1, 30, 2, device))
+    attempt("single_search_c4_acp_prodigal_4x256_2000steps", lambda: timed_search("c4", "acp_prodigal", 4, 256, 2000, 1, 0, 3, device))
+    for warps in (8, 1):
+        a = copy.copy(args)
+        a.puct_warps, a.steps, a.warmup = warps, 5, 3
+
+        def puct(a=a):
+            line = run_puct(a)
+            return {k: line[k] for k in ("value", "unit", "ms_per_step", "config", "valid_selections", "virtual_loss_1",
+                                         "reference_kernel", "roofline")}
+        attempt(f"puct_select_{warps}_warps", puct)
+    a = copy.copy(args)
+    a.steps, a.warmup, a.no_cpu_baseline = 5, 3, True
+    attempt("duct_select_8_warps", lambda: {k: v for k, v in run_duct(a).items() if k in ("value", "unit", "ms_per_step", "config", "mean_path_length", "busy_fraction", "roofline")})
+    if os.path.exists(os.path.join(REF_SRC, "mctsnc.py")):
+        out["reference_cpu_mcts"] = run_child("reference-mcts", args, ["--roots", str(args.roots)], 300)
+        out["reference_numba_cuda_on_this_gpu"] = run_child("reference-numba", args, ["--roots", "4"], 420)
+    else:
+        why = {"unavailable": "no copy of the reference under baseline/_ref (python baseline/install_reference.py)"}
+        out["reference_cpu_mcts"], out["reference_numba_cuda_on_this_gpu"] = why, why
+    return out
+
+
+def multi_gpu_parity(args, searcher, boards, fills, turns, rank, world, local_rank):
+    """Root-parallel result against one GPU growing all the trees: every rank searches 4 roots for 100 steps with its own
+    shard of the world * n_trees trees; rank 0 then grows all world * n_trees trees itself and compares the all-reduced
+    sums and the chosen action.  Outside every timed region."""
+    from mcts_numba_cuda_b200 import MCTSNC
+    G = GAMES[args.game]
+    A, roots, steps = G["actions"], 4, 100
+    got = searcher.run_batch(boards[:roots], None if fills is None else fills[:roots], turns[:roots], steps, reseed=True)
+    if rank != 0:
+        return None
+    whole = MCTSNC(G["shape"], G["extra"], A, search_time_limit=np.inf, search_steps_limit=steps, n_trees=args.trees * world,
+                   n_playouts=args.playouts, variant=args.variant, verbose_info=False, device=local_rank, max_batch=roots, seed=0,
+                   ucb_c=2.0, device_memory=16.0 if args.game == "gomoku" else 2.0)
+    whole.init_device_side_arrays()
+    want = whole.run_batch(boards[:roots], None if fills is None else fills[:roots], turns[:roots], steps, reseed=True)
+    same = all(np.array_equal(got[k][:, :A] if got[k].ndim > 1 else got[k], want[k][:, :A] if want[k].ndim > 1 else want[k])
+               for k in ("root_ns", "actions_ns", "actions_ns_wins", "best_action", "best_n", "best_n_wins", "best_win_flag"))
+    return bool(same)
 
 
 def main():
     args = parse_args()
+    if args.internal == "reference-mcts":
+        internal_reference_mcts(args)
+        return
+    if args.internal == "reference-numba":
+        internal_reference_numba(args)
+        return
     if args.workload == "puct":
-        run_puct(args)
+        print(json.dumps(run_puct(args)))
         return
     if args.workload == "duct":
-        run_duct(args)
+        print(json.dumps(run_duct(args)))
         return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -449,6 +678,7 @@ def main():
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
+    parity = multi_gpu_parity(args, searcher, boards, fills, turns, rank, world, local_rank) if world > 1 else None
     # max over ranks of the timed regions, sums of the work
     stats = torch.tensor([dev_ms, e2e_s * 1e3, kernel_ms], dtype=torch.float64, device="cuda")
     work = torch.tensor([local_playouts, local_plies], dtype=torch.int64, device="cuda")
@@ -464,28 +694,27 @@ def main():
     pk = peaks()
     value = playouts_per_pass * args.steps / (dev_ms * 1e-3)
     e2e_value = playouts_per_pass * args.steps / (e2e_ms * 1e-3)
-    thr, per_sm, sms, nbytes = (np.zeros(1, np.int32), np.zeros(1, np.int32), np.zeros(1, np.int32), np.zeros(1, np.int64))
-    import ctypes
-    _abi.lib().mctsnc_query(searcher.local._handle, thr.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
-                            per_sm.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
-                            sms.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)),
-                            nbytes.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)))
-    sm_count = int(sms[0])
+    geo = searcher.local.launch_geometry()
+    sm_count, per_sm = geo["sm_count"], geo["blocks_per_sm"]
     # dominant kernel: the search kernel.  Per rank and launch it plays plies_per_pass / n_gpus plies.
     plies_per_launch = plies_per_pass / n_gpus
     playouts_per_launch = playouts_per_pass / n_gpus
     tree_steps_per_launch = B * args.trees * args.search_steps
-    # algorithmic HBM bytes: every stream state is read and written once per launch (2 x 16 B), and a
-    # tree-step touches ~1.3 KB of tree records
-    # A Connect-4 batch with more trees than resident blocks runs in slices of 32 steps taken from a work queue; a
-    # tree's streams are then read and written once per slice (they fit in L2 between slices for the headline batch).
-    queued = args.game == "c4" and B * args.trees > int(per_sm[0]) * sm_count and args.search_steps > 32
+    # algorithmic HBM bytes: a tree-step touches ~1.3 KB of tree records; every stream state is read and written once
+    # per launch, or once per 32-step slice when a Connect-4 batch with more trees than resident blocks runs through the
+    # work queue (the streams of the headline batch stay in L2 between slices)
+    queued = args.game == "c4" and B * args.trees > per_sm * sm_count and args.search_steps > 32
     slices = -(-args.search_steps // 32) if queued else 1
     n_streams = B * args.trees * (A if "acp" in args.variant else 1) * args.playouts
     algo_bytes = 32.0 * n_streams * slices + 1300.0 * tree_steps_per_launch
     hbm_achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+    # the binding roofline: instruction issue.  Work unit = one playout ply, yardstick thread instructions per ply;
+    # peak = SMs x 4 schedulers x 32 lanes x SM clock
     peak_inst = sm_count * 4 * 32 * pk["sm_max_mhz"] * 1e6
     inst_achieved = plies_per_launch * G["inst_per_ply"] / (kernel_ms * 1e-3)
+    workload_key = f"{args.variant},{args.trees},{args.playouts},{args.search_steps},{B}"
+    prof = profiler_readings(args.game, workload_key)
+    kernel_name = "c4::search_kernel" if args.game == "c4" else "gomoku::playout_dynamic_kernel (+ tree_step_kernel)"
     line = {
         "metric": "playouts/sec", "value": value, "unit": "playouts/s", "n_gpus": n_gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -493,33 +722,36 @@ def main():
         "e2e": {"value": e2e_value, "unit": "playouts/s", "h2d_bytes_per_step": int(B * (17 if args.game == "c4" else 65)),
                 "d2h_bytes_per_step": int(B * (3 * A * 8 + 2 * A + 80)), "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": args.steps * ((6 if queued else 4) if args.game == "c4" else 4 + 2 * args.search_steps),
-        "roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": hbm_achieved / pk["hbm_gbs"],
-                     "traffic": MEASURED_TRAFFIC_BYTES.get((args.game, args.variant, args.trees, args.playouts, args.search_steps, B)),
-                     "traffic_unit": "bytes per launch (ncu, one capture)", "algorithmic_bytes": algo_bytes,
-                     "peak_source": pk["source"],
-                     "kernel": "c4::search_kernel" if args.game == "c4" else "gomoku::playout_kernel (+ tree_step_kernel)", "kernel_ms": kernel_ms,
-                     "note": "the search is instruction-issue bound, not HBM bound: see issue_roofline"},
-        "issue_roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12,
-                           "unit": "T thread-inst/s", "frac": inst_achieved / peak_inst,
-                           "binding_unit": ("integer/logic pipe (16 lanes per clock and scheduler): 87.8 % of its peak, 71.5 % of "
-                                            "issue slots, 21.9 of 32 lanes active (ncu capture of the 256-root, 200-step case)"
-                                            if args.game == "c4" else
-                                            "integer/logic pipe: 76.4 % of its peak, 72.0 % of issue slots, 21.2 of 32 lanes active "
-                                            "(ncu capture of one step of a 4 x 256 search)"),
-                           "plies_per_playout": plies_per_launch / max(playouts_per_launch, 1),
-                           "inst_per_ply_yardstick": G["inst_per_ply"], "sm_count": sm_count,
-                           "peak_clock_mhz": pk["sm_max_mhz"]},
-        "clocks": clocks, "threads_per_tree": int(thr[0]), "blocks_per_sm": int(per_sm[0]),
-        "device_bytes": int(nbytes[0]), "status_bits": status, "ub_draws_per_pass": ub_draws,
+        "roofline": {"bound": "issue", "achieved": inst_achieved / 1e12, "peak": peak_inst / 1e12, "unit": "T thread-inst/s",
+                     "frac": inst_achieved / peak_inst, "peak_source": f"{sm_count} SMs x 4 schedulers x 32 lanes x {pk['sm_max_mhz']:.0f} MHz ({pk['source']} clock)",
+                     "traffic": None if prof is None else prof.get("dram_bytes_per_launch"),
+                     "traffic_unit": "DRAM bytes per launch (ncu)", "kernel": kernel_name, "kernel_ms": kernel_ms,
+                     "work_unit": "playout ply", "inst_per_ply_yardstick": G["inst_per_ply"],
+                     "plies_per_playout": plies_per_launch / max(playouts_per_launch, 1), "plies_per_launch": plies_per_launch,
+                     "profiler": None if prof is None else {k: prof.get(k) for k in ("case", "alu_pipe_pct", "issue_active_pct",
+                                                                                        "lanes_per_instruction", "thread_inst_per_ply")},
+                     "note": "integer, branch-heavy work without a dense contraction: the limit is instruction issue, not HBM (hbm_roofline)"},
+        "hbm_roofline": {"bound": "hbm", "achieved": hbm_achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": hbm_achieved / pk["hbm_gbs"], "algorithmic_bytes": algo_bytes, "peak_source": pk["source"]},
+        "clocks": clocks, "threads_per_tree": geo["threads_per_tree"], "blocks_per_sm": per_sm,
+        "device_bytes": geo["device_bytes"], "status_bits": status, "ub_draws_per_pass": ub_draws,
         "playouts_per_pass": playouts_per_pass, "best_action_checksum": int(out["best_action"].astype(np.int64).sum()),
+        "multi_gpu_parity": parity,
     }
     if n_gpus == 1 and not args.no_cpu_baseline:
-        steps = args.cpu_sample_steps
+        steps = args.cpu_sample_steps or 400
         n_roots = args.cpu_sample_roots or 8
         playouts, plies, wall = cpu_port_baseline(args, boards, fills, turns, 1, n_roots, steps)
         line["cpu_baseline"] = {"value": playouts / wall, "unit": "playouts/s", "cores": 1, "kind": "port",
                                 "sample": f"{n_roots} roots x {steps} search steps, sequential, {wall:.1f} s"}
+    if n_gpus == 1 and not args.no_secondary:
+        del searcher
+        torch.cuda.empty_cache()
+        line["secondary"] = secondary_runs(args, local_rank)
+        ref_cpu = line["secondary"].get("reference_cpu_mcts", {})
+        if "cpu_baseline" in line and "one_core" in ref_cpu:
+            line["cpu_baseline"]["reference_mcts"] = {"one_core": ref_cpu["one_core"], "all_cores": ref_cpu["all_cores"],
+                                                      "what": ref_cpu["what"]}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -76,6 +76,7 @@ typedef struct mo_ctx {
     int64_t cap;           /* nodes actually allocated per tree */
     float ucb_c;
     uint64_t seed;
+    int64_t tree_offset;       /* global index of this context's first tree (0 unless the search is split) */
     int tpb_r, tpb_s, tpb_e1, tpb_e2, tpb_b1, tpb_b2, tpb_rot, tpb_roa;
     /* device-side arrays of the reference, src/mctsnc.py:372-404 */
     int32_t *trees;
@@ -156,15 +157,19 @@ static void rng_jump(rng_state *s) {
     s->s1 = s1;
 }
 
-/* init_xoroshiro128p_states_cpu with subsequence_start = 0 */
-void mo_rng_init_states(rng_state *states, int64_t n, uint64_t seed) {
+/* init_xoroshiro128p_states_cpu(states, seed, subsequence_start): state 0 is the seeded state jumped
+ * subsequence_start times, state i the state i-1 jumped once more (numba/cuda/random.py:226-243) */
+void mo_rng_init_states_from(rng_state *states, int64_t n, uint64_t seed, int64_t subsequence_start) {
     if (n < 1) return;
     rng_seed(&states[0], seed);
+    for (int64_t i = 0; i < subsequence_start; i++) rng_jump(&states[0]);
     for (int64_t i = 1; i < n; i++) {
         states[i] = states[i - 1];
         rng_jump(&states[i]);
     }
 }
+
+void mo_rng_init_states(rng_state *states, int64_t n, uint64_t seed) { mo_rng_init_states_from(states, n, seed, 0); }
 
 /* xoroshiro128p_uniform_float32: float32(float64(x >> 11) * 2^-53) */
 static inline float rng_uniform_f32(rng_state *s) {
@@ -763,10 +768,19 @@ mo_ctx *mo_create(int m, int n, int extra, int A, int game, int T, int P, int va
     return c;
 }
 
-/* init_device_side_arrays() re-creates the generators, src/mctsnc.py:390-394 */
+/* init_device_side_arrays() re-creates the generators, src/mctsnc.py:390-394.  With a tree offset the context grows the
+ * trees [offset, offset + T) of a larger search: tree t of the context draws from the streams tree offset + t has in the
+ * reference's arrays (stream index tree * A * P + action * P + thread, :1938, :2028; OCP: tree * P + thread and
+ * tree * tpb_e1), which is how a search is split over several devices without changing its result. */
 void mo_reset_rng(mo_ctx *c) {
-    mo_rng_init_states(c->rng_expand_1, c->n_rng_expand_1, c->seed);
-    mo_rng_init_states(c->rng_playout, c->n_rng_playout, c->seed);
+    int64_t per_tree = c->n_rng_playout / c->T;
+    mo_rng_init_states_from(c->rng_expand_1, c->n_rng_expand_1, c->seed, c->tree_offset * (int64_t)c->tpb_e1);
+    mo_rng_init_states_from(c->rng_playout, c->n_rng_playout, c->seed, c->tree_offset * per_tree);
+}
+
+void mo_set_tree_offset(mo_ctx *c, int64_t tree_offset) {
+    c->tree_offset = tree_offset;
+    mo_reset_rng(c);
 }
 
 void mo_destroy(mo_ctx *c) {

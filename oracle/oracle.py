@@ -67,6 +67,7 @@ def lib():
         L.mo_create.argtypes = [ctypes.c_int] * 8 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_uint64]
         L.mo_destroy.argtypes = [ctypes.c_void_p]
         L.mo_reset_rng.argtypes = [ctypes.c_void_p]
+        L.mo_set_tree_offset.argtypes = [ctypes.c_void_p, ctypes.c_int64]
         L.mo_run.restype = ctypes.c_int
         L.mo_run.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                              ctypes.c_int64, ctypes.c_void_p]
@@ -127,7 +128,7 @@ class OracleMCTSNC:
 
     def __init__(self, state_board_shape, state_extra_info_memory, state_max_actions, n_trees=8, n_playouts=128,
                  variant="acp_prodigal", device_memory=2.0, ucb_c=2.0, seed=0, game=None, max_tree_size=None,
-                 node_capacity=None):
+                 node_capacity=None, tree_offset=0, n_trees_global=None):
         self.m, self.n = state_board_shape
         self.extra = max(state_extra_info_memory, 1)
         self.A = state_max_actions
@@ -136,14 +137,19 @@ class OracleMCTSNC:
         if game is None:
             game = GAME_C4 if self.A == self.n else GAME_GOMOKU
         self.game = game
+        # a context that grows the trees [tree_offset, tree_offset + n_trees) of a search with n_trees_global trees
+        self.tree_offset = int(tree_offset)
+        self.n_trees_global = int(n_trees_global) if n_trees_global is not None else self.tree_offset + n_trees
         self.max_tree_size = max_tree_size if max_tree_size is not None else reference_max_tree_size(
-            state_board_shape, state_extra_info_memory, state_max_actions, n_trees, variant, device_memory)
+            state_board_shape, state_extra_info_memory, state_max_actions, self.n_trees_global, variant, device_memory)
         cap = node_capacity if node_capacity is not None else min(self.max_tree_size, 1 << 16)
         self._ctx = lib().mo_create(self.m, self.n, self.extra, self.A, game, self.T, self.P, VARIANTS.index(variant),
                                     self.max_tree_size, cap, ucb_c, ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF))
         if not self._ctx:
             raise MemoryError("oracle allocation failed")
         self.cap = lib().mo_cap(self._ctx)
+        if self.tree_offset:
+            lib().mo_set_tree_offset(self._ctx, self.tree_offset)
 
     def __del__(self):
         if getattr(self, "_ctx", None):

@@ -1,7 +1,7 @@
-"""The multi-GPU (root-parallel) host logic on CPU: two gloo ranks each take half of the trees of a search, form the
-partial per-action sums of their trees, all-reduce them and run the final argmax; the result must equal the unsharded
-search.  The trees themselves come from the CPU oracle here (no GPU): trees are independent, so rank r's partial sums
-are the sums over the slice [r*T, (r+1)*T) of the trees of the search with all trees."""
+"""The multi-GPU (root-parallel) path on CPU: two gloo ranks each GROW half of the trees of a search (the CPU oracle
+with a tree offset, i.e. with the random streams those trees have in the unsharded search -- what a rank's handle does
+on its GPU), form the partial per-action sums of their own trees, all-reduce them and run the final argmax; the result
+must equal the unsharded search, which every rank also runs for comparison."""
 import os
 import socket
 
@@ -46,13 +46,21 @@ def _worker(rank, world, port, variant, out_dir):
         orc = OracleMCTSNC((6, 7), 7, 7, n_trees=T_global, n_playouts=32, variant=variant, seed=3, node_capacity=steps * 7 + 8)
         orc.run(np.zeros((6, 7), np.int8), np.zeros(7, np.int8), 1, steps)
         offset, local = shard_trees(T_global, world, rank)
-        sums, expanded = _partial_sums(orc, offset, offset + local)
+        mine = OracleMCTSNC((6, 7), 7, 7, n_trees=local, n_playouts=32, variant=variant, seed=3, node_capacity=steps * 7 + 8,
+                            tree_offset=offset, n_trees_global=T_global)
+        mine.run(np.zeros((6, 7), np.int8), np.zeros(7, np.int8), 1, steps)
+        sums, expanded = _partial_sums(mine, 0, local)
+        for t in range(local):      # the shard's trees are the trees [offset, offset + local) of the unsharded search
+            n = orc.field("trees_sizes")[offset + t]
+            assert mine.field("trees_sizes")[t] == n
+            assert np.array_equal(mine.field("trees_ns")[t, :n], orc.field("trees_ns")[offset + t, :n])
+            assert np.array_equal(mine.field("trees_ns_wins")[t, :n], orc.field("trees_ns_wins")[offset + t, :n])
         t = torch.from_numpy(sums)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         total = t.numpy()
         A = orc.A
-        best = reduce_over_actions_host(orc.field("actions_win_flags") if "prodigal" in variant else
-                                        _flags_by_action(orc), total[A:2 * A], total[2 * A:], expanded, "thrifty" in variant)
+        best = reduce_over_actions_host(mine.field("actions_win_flags") if "prodigal" in variant else
+                                        _flags_by_action(mine), total[A:2 * A], total[2 * A:], expanded, "thrifty" in variant)
         ok = best == (orc.best_action, orc.best_win_flag, orc.best_n, orc.best_n_wins)
         root_ok = np.array_equal(total[:A][expanded], np.full(int(expanded.sum()), orc.playouts))
         np.save(os.path.join(out_dir, f"ok_{rank}.npy"), np.array([ok, root_ok]))

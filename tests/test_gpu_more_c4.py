@@ -119,10 +119,22 @@ def test_json_dump_has_the_reference_keys(tmp_path):
     assert np.array(d["trees"]).shape == (2, max(d["trees_sizes"]), 8)
 
 
+def _oracle_headline_search(job):
+    board, fills, turn, steps = job
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=4, n_playouts=256, variant="acp_prodigal", seed=0, node_capacity=steps * 7 + 8)
+    orc.run(board, fills, int(turn), steps)
+    return orc
+
+
 def test_full_size_headline_workload_invariants():
-    """256 roots x 4 trees x 256 playouts x 2000 steps: checked through properties that hold at any size."""
+    """256 roots x 4 trees x 256 playouts x 2000 steps (the benchmark's batch, run through the work queue): three of
+    its searches are compared with the oracle field by field, all of them through properties that hold at any size."""
+    from concurrent.futures import ThreadPoolExecutor
     B, steps = 256, 2000
     boards, fills, turns = c4_random_roots(B, 20, seed=0)
+    checked = (0, 101, 255)
+    pool = ThreadPoolExecutor(max_workers=len(checked))     # about 16 s each on a host core, while the GPU works
+    oracles = [pool.submit(_oracle_headline_search, (boards[b], fills[b], turns[b], steps)) for b in checked]
     ai = MCTSNC((6, 7), 7, 7, search_time_limit=np.inf, search_steps_limit=steps, n_trees=4, n_playouts=256,
                 variant="acp_prodigal", verbose_info=False, max_batch=B)
     ai.init_device_side_arrays()
@@ -157,6 +169,17 @@ def test_full_size_headline_workload_invariants():
             win_sum = np.bincount(par, weights=wins[t, 1:n], minlength=n).astype(np.int64)
             assert (wins[t, :n][inner] + win_sum[inner] <= ns[t, :n][inner]).all()      # the rest are draws
             assert n == 1 + int((trees[t, :n, 1:] >= 0).sum())
+    geo = ai.launch_geometry()
+    assert B * 4 > geo["blocks_per_sm"] * geo["sm_count"]            # the batch went through the work queue
+    for b, fut in zip(checked, oracles):
+        orc = fut.result()
+        compare_trees(ai, orc, search=b)
+        assert out["best_action"][b] == orc.best_action and out["best_n"][b] == orc.best_n
+        assert out["best_n_wins"][b] == orc.best_n_wins and out["playouts"][b] == orc.playouts
+        assert out["plies"][b] == orc.plies and out["ub_draws"][b] == orc.ub_draws
+        assert np.array_equal(out["actions_ns"][b, :7], orc.field("actions_ns"))
+        assert np.array_equal(out["actions_ns_wins"][b, :7], orc.field("actions_ns_wins"))
+    pool.shutdown()
     # a search does not depend on its position in the batch
     perm = np.random.default_rng(1).permutation(B)
     short = ai.run_batch(boards, fills, turns, steps=100, reseed=True)

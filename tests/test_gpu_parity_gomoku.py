@@ -75,6 +75,31 @@ def test_gomoku_random_roots_match_oracle(variant):
         assert int(best) == orc.best_action
 
 
+@pytest.mark.parametrize("variant,root_index", [("acp_prodigal", 0), ("acp_thrifty", 1)])
+def test_gomoku_headline_shape_4_trees_256_playouts_matches_oracle(variant, root_index):
+    """The launch shape of BASELINE's Gomoku configuration (4 trees x 256 playouts, device_memory 16 GiB): up to 225
+    children x 256 games per tree and step through the persistent playout grid, compared with the oracle field by field
+    after 8 steps.  The oracle searches run on host threads meanwhile (the ctypes calls release the interpreter lock)."""
+    from concurrent.futures import ThreadPoolExecutor
+    steps = 8
+    boards, turns = gomoku_random_roots(2, 30, seed=11)
+    board, turn = boards[root_index], int(turns[root_index])
+    ai, orc = make_pair(variant, 4, 256, steps, seed=0)
+    with ThreadPoolExecutor(max_workers=1) as ex:
+        fut = ex.submit(orc.run, board, None, turn, steps)
+        best = ai.run(board, None, turn)
+        again = ai.run(board, None, turn)      # streams run on: a different search, must still be a valid one
+        fut.result()
+    assert ai.status & 4 == 0 and int(again) >= 0
+    ai.reset_random_streams()
+    best2 = ai.run(board, None, turn)
+    assert int(best2) == int(best)
+    compare(ai, orc)
+    assert int(best) == orc.best_action
+    assert (ai.best_win_flag, int(ai.best_n), int(ai.best_n_wins)) == (orc.best_win_flag, orc.best_n, orc.best_n_wins)
+    assert ai._res["playouts"] == orc.playouts and ai._res["plies"] == orc.plies and ai._res["ub_draws"] == orc.ub_draws
+
+
 def nearly_full_board(n_empty, seed):
     """A 15x15 position without any line of five (stones in an XXOO pattern shifted by two per row) with n_empty holes."""
     i, j = np.meshgrid(np.arange(15), np.arange(15), indexing="ij")
