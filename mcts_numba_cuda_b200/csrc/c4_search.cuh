@@ -28,6 +28,7 @@ constexpr int PLIES_PER_CHECK = MCTSNC_PLIES_PER_CHECK;  // plies of a playout b
 constexpr unsigned long long BOTTOM_ROW = 0x0000040810204081ULL;  // bit 7c for c = 0..6
 constexpr unsigned long long TOP_ROW = BOTTOM_ROW << 5;
 constexpr unsigned long long FULL_BOARD = BOTTOM_ROW * 0x3FULL;
+constexpr unsigned long long MOVE_LUT_NO_COLUMN = 1ULL << 63;
 
 // four in a row anywhere in the stone set p.  Left shifts: the low word of a 64-bit left shift is a plain 32-bit
 // shift, which the integer multiply-add pipe can execute, taking load off the logic pipe that limits this kernel.
@@ -178,7 +179,7 @@ __device__ __noinline__ EmuResult playout_emulated(unsigned long long neg, unsig
 // everything a thread needs to start a game from one child, fetched with two 16-byte shared-memory loads
 struct __align__(16) GameSlot {
     unsigned long long cur;  // stones of the side to move
-    unsigned long long all;  // all stones
+    unsigned long long top;  // one bit per column: its lowest empty cell (the guard bit of a full column) = all stones + BOTTOM_ROW
     unsigned legal;          // columns with room, shifted left by LEGAL_SHIFT
     int rng_base;            // index of the child's first stream in the block's stream array
     int stones;              // stones on the board
@@ -196,9 +197,10 @@ struct Shared {
     int child_slot[A];       // and its slot (-1: no playouts: terminal, or not picked in OCP)
     int child_out[A][2];     // trees_playout_outcomes_children (persists over steps)
     short ae[A + 2];         // trees_actions_expanded row (persists over steps)
-    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the bottom cell of the column
-    // (bit 7 * column) in bits 0..47 and the column's bit in bits 54..60, i.e. where it sits in the pre-shifted column
-    // set the playout loop keeps (GameSlot::legal), moved up by 48
+    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the seven bits of the column
+    // (0x7F << 7 * column) in bits 0..48 and the column's bit in bits 54..60, i.e. where it sits in the pre-shifted column
+    // set the playout loop keeps (GameSlot::legal), moved up by 48.  An ordinal the set does not have (only a uniform
+    // draw of exactly 1.0f gives one: ord == number of columns) maps to MOVE_LUT_NO_COLUMN: no cell, bit 63 set.
     unsigned long long move_lut[128 * 8];
     int job;                 // tree of the slice being run (-1: none left)
     int n_slots;
@@ -395,7 +397,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         if (plays) {
                             GameSlot gs;
                             gs.cur = sel_turn > 0 ? cneg : cpos;  // the child is to be moved in by the other side
-                            gs.all = call;
+                            gs.top = call + BOTTOM_ROW;
                             gs.legal = legal_columns(call) << LEGAL_SHIFT;
                             gs.rng_base = OCP ? 0 : lane * P;
                             gs.stones = __popcll(call);
@@ -412,7 +414,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                     if (lane == 0) {
                         GameSlot gs;
                         gs.cur = sel_turn > 0 ? bb.y : bb.x;
-                        gs.all = all;
+                        gs.top = all + BOTTOM_ROW;
                         gs.legal = legal << LEGAL_SHIFT;
                         gs.rng_base = 0;
                         gs.stones = __popcll(all);
@@ -461,14 +463,18 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         // until the step's games run out whatever their lengths.  Game `item` is playout t = item % P of slot
         // item / P; it draws from the stream the reference's thread (tree, action, t) owns (src/mctsnc.py:1938, :2028;
         // OCP: cuda.grid(1), :1849), so which thread plays it does not matter.
+        //
+        // The board of a game in progress is three words: the stones of the side that moves at the even plies of a
+        // block of PLIES_PER_CHECK plies (a game starts at ply 0 of a block, so that is the side to move in the game's
+        // first position), the stones of the other side, and `top`, one bit per column at its lowest empty cell (the
+        // guard bit once the column is full; top = all stones + BOTTOM_ROW).  A move in column c is then
+        // top & (seven bits of column c), and top + move puts the marker one cell up.
         {
             const int n_items = s.n_slots << p.log2_playouts;
             // the side to move in the played-out positions: the other side than at the selected node, unless the
             // selected node itself is played out
             const int first_mover = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
-            // stones of the side that moves at the even plies of a block of PLIES_PER_CHECK plies (a game starts at ply 0 of a
-            // block, so that is the side to move in the game's first position), stones of the other side, all stones
-            unsigned long long side_even = 0, side_odd = 0, all = 0, s0 = 0, s1 = 0;
+            unsigned long long side_even = 0, side_odd = 0, top = 0, s0 = 0, s1 = 0;
             unsigned legal = 0;
             float count = 0.f;
             int rng_idx = 0, stones = 0, j = 0;
@@ -477,8 +483,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 j = item >> p.log2_playouts;
                 const GameSlot gs = s.slot[j];
                 side_even = gs.cur;
-                side_odd = gs.all ^ gs.cur;
-                all = gs.all;
+                side_odd = (gs.top - BOTTOM_ROW) ^ gs.cur;
+                top = gs.top;
                 legal = gs.legal;
                 count = gs.count;
                 stones = gs.stones;
@@ -494,70 +500,66 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 // iteration; checking after every fourth ply costs a little lane time and saved 10 % of the run time
                 // (13.8 -> 15.3 G playouts/s on the headline workload; 2: 14.9, 3: 15.3, 5: 15.4, 8: 14.1).
                 bool win = false, over = false;
-                int emu_outcome = 2;
+                unsigned no_column = 0;   // bit 31 set once a draw of 1.0f asked for a column the position does not have
                 static_assert(PLIES_PER_CHECK % 2 == 0, "the two sides alternate by the parity of the ply within a block");
 #pragma unroll
                 for (int k = 0; k < PLIES_PER_CHECK; k++) {
                     if (over) continue;
                     // ---- one ply (src/mctsnc.py:2059-2064, :2069)
-                    // float32 u * int16 count -> float32 (:2061); here (u * 2^64) * (count * 2^-64): the same product
+                    // float32 u * int16 count -> float32 (:2061); here (u * 2^64) * (count * 2^-64): the same product.
+                    // u == 1.0f gives ord == count, which the table answers with MOVE_LUT_NO_COLUMN: nothing is played, the flag
+                    // sticks, and the game is replayed from its start through the byte-level emulation when it is closed
                     const float f = rng_uniform_times_2p64(s0, s1);
-                    const float prod = __fmul_rn(f, count);
-                    if (f >= RNG_2P64) {
-                        // u == 1.0f: replay this game through the byte-level emulation of the reference
+                    const int ord = __float2int_rz(__fmul_rn(f, count));
+                    const unsigned long long e = *reinterpret_cast<const unsigned long long *>(
+                        reinterpret_cast<const char *>(s.move_lut) + (legal + ord * 8));
+                    no_column |= (unsigned)(e >> 32);
+                    const unsigned long long move = top & e;
+                    top += move;
+                    // the sides take turns with the plies of the unrolled block: no swap of "mine" and "theirs"
+                    unsigned long long mine;
+                    if (k & 1) {
+                        side_odd |= move;
+                        mine = side_odd;
+                    } else {
+                        side_even |= move;
+                        mine = side_even;
+                    }
+                    win = has_four(mine);
+                    if ((move & TOP_ROW) != 0) {
+                        legal ^= (unsigned)(e >> 48);
+                        count -= RNG_2M64;
+                    }
+                    over = win || count == 0.0f;
+                }
+                if (over || (no_column & 0x80000000u)) {
+                    int n = __popcll(side_even | side_odd) - stones;  // plies of this game; the last one was made by the
+                    int winner = 0;                                    // first mover iff n is odd
+                    if (win) winner = (n & 1) ? first_mover : -first_mover;
+                    if (no_column & 0x80000000u) {
+                        // u == 1.0f somewhere in this game: replay it through the byte-level emulation of the reference
                         const GameSlot gs = s.slot[j];
                         const ulonglong2 rs = s_rng[rng_idx];
-                        const unsigned long long other = gs.all ^ gs.cur;
+                        const unsigned long long other = (gs.top - BOTTOM_ROW) ^ gs.cur;
                         const EmuResult er = playout_emulated(first_mover > 0 ? other : gs.cur, first_mover > 0 ? gs.cur : other,
                                                               first_mover, rs.x, rs.y);
                         s0 = er.s0;
                         s1 = er.s1;
-                        emu_outcome = er.outcome;
-                        my_plies += er.plies;
+                        winner = er.outcome == 2 ? 0 : er.outcome;
+                        n = (int)er.plies;
                         my_ub += er.ub;
                         my_err |= er.err;
-                        all = 0;  // the plies of the replay are counted above, none from the bitboards
-                        stones = 0;
-                        win = false;
-                        over = true;
-                    } else {
-                        const int ord = __float2int_rz(prod);
-                        const unsigned long long e = *reinterpret_cast<const unsigned long long *>(
-                            reinterpret_cast<const char *>(s.move_lut) + (legal + ord * 8));
-                        const unsigned long long nall = all | (all + (e & 0x0000FFFFFFFFFFFFULL));
-                        const unsigned long long move = nall ^ all;
-                        // the sides take turns with the plies of the unrolled block: no swap of "mine" and "theirs"
-                        unsigned long long mine;
-                        if (k & 1) {
-                            side_odd |= move;
-                            mine = side_odd;
-                        } else {
-                            side_even |= move;
-                            mine = side_even;
-                        }
-                        all = nall;
-                        win = has_four(mine);
-                        if ((move & TOP_ROW) != 0) {
-                            legal ^= (unsigned)(e >> 48);
-                            count -= RNG_2M64;
-                        }
-                        over = win || count == 0.0f;
                     }
-                }
-                if (over) {
                     s_rng[rng_idx] = make_ulonglong2(s0, s1);
-                    const int n = __popcll(all) - stones;  // plies of this game; the last one was made by the first
-                    my_plies += n;                         // mover iff n is odd
-                    int winner = emu_outcome == 2 ? 0 : emu_outcome;
-                    if (win) winner = (n & 1) ? first_mover : -first_mover;
+                    my_plies += n;
                     if (winner != 0) atomicAdd(&s.tally[j][winner > 0 ? 1 : 0], 1);
                     item = atomicAdd(&s.next_item, 1);
                     if (item < n_items) {
                         j = item >> p.log2_playouts;
                         const GameSlot gs = s.slot[j];
                         side_even = gs.cur;
-                        side_odd = gs.all ^ gs.cur;
-                        all = gs.all;
+                        side_odd = (gs.top - BOTTOM_ROW) ^ gs.cur;
+                        top = gs.top;
                         legal = gs.legal;
                         count = gs.count;
                         stones = gs.stones;
@@ -682,13 +684,14 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
     const int tid = threadIdx.x;
     for (int i = tid; i < 128 * 8; i += blockDim.x) {
         const int set = i >> 3, ord = i & 7;
-        int col = 0, seen = 0;
+        int col = -1, seen = 0;
         for (int c = 0; c < COLS; c++)
             if (set & (1 << c)) {
                 if (seen == ord) col = c;
                 seen++;
             }
-        s.move_lut[i] = (1ULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
+        s.move_lut[i] = col < 0 ? MOVE_LUT_NO_COLUMN
+                                : (0x7FULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
     }
     const bool queued = p.queue != nullptr;
     for (;;) {

@@ -53,7 +53,7 @@ MAX_TREE_DEPTH = 2048
 TPB = {"r": 256, "s": 512, "e2": 256, "b1": 256, "b2": 512, "roa": 256}   # tpb table of src/mctsnc.py:360-370 for 15x15, 225 actions
 
 # name: (trees, playouts, stones on the root board, seed of the root, seed of the search)
-CASES = {"late": (2, 32, 160, 5, 0), "middle": (1, 32, 96, 6, 3)}
+CASES = {"late": (2, 32, 160, 5, 0), "middle": (1, 32, 96, 6, 3), "early": (2, 8, 12, 7, 1)}
 
 
 def random_root(stones, seed):
