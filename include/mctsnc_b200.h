@@ -91,6 +91,11 @@ typedef struct mctsnc_result {
     int64_t depth_sum;           /* sum of node depths over all nodes (for mean_depth) */
     int32_t max_size;
     int32_t reserved;
+    /* time spent in the four stages of the steps (select, expand, playouts, backup), milliseconds, mean over this
+       handle's trees of the time their blocks spent there (SM cycle counter at the nominal clock); the reference's
+       time_select / time_expand / time_playout / time_backup (src/mctsnc.py:606-686) are host clocks around launches */
+    float stage_ms[4];
+    float reduce_ms[2];          /* CUDA-event time of the two final reductions (mctsnc_run only; 0 for batch calls) */
     int64_t root_ns[MCTSNC_MAX_ACTIONS];         /* sum over trees of the root visit count, 0 for actions not expanded */
     int64_t actions_ns[MCTSNC_MAX_ACTIONS];
     int64_t actions_ns_wins[MCTSNC_MAX_ACTIONS];

@@ -45,7 +45,7 @@ class Result(ctypes.Structure):
                 ("plies", ctypes.c_int64), ("ub_draws", ctypes.c_int64), ("status", ctypes.c_uint32),
                 ("n_root_actions", ctypes.c_int32), ("device_ms", ctypes.c_float), ("max_depth", ctypes.c_int32),
                 ("total_nodes", ctypes.c_int64), ("depth_sum", ctypes.c_int64), ("max_size", ctypes.c_int32),
-                ("reserved", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("stage_ms", ctypes.c_float * 4), ("reduce_ms", ctypes.c_float * 2),
                 ("root_ns", ctypes.c_int64 * MAX_ACTIONS), ("actions_ns", ctypes.c_int64 * MAX_ACTIONS),
                 ("actions_ns_wins", ctypes.c_int64 * MAX_ACTIONS), ("actions_win_flags", ctypes.c_uint8 * MAX_ACTIONS),
                 ("actions_expanded", ctypes.c_uint8 * MAX_ACTIONS)]
@@ -56,6 +56,7 @@ RESULT_DTYPE = np.dtype([("best_action", np.int32), ("best_win_flag", np.int32),
                          ("ub_draws", np.int64), ("status", np.uint32), ("n_root_actions", np.int32),
                          ("device_ms", np.float32), ("max_depth", np.int32), ("total_nodes", np.int64),
                          ("depth_sum", np.int64), ("max_size", np.int32), ("reserved", np.int32),
+                         ("stage_ms", np.float32, (4,)), ("reduce_ms", np.float32, (2,)),
                          ("root_ns", np.int64, (MAX_ACTIONS,)), ("actions_ns", np.int64, (MAX_ACTIONS,)),
                          ("actions_ns_wins", np.int64, (MAX_ACTIONS,)), ("actions_win_flags", np.uint8, (MAX_ACTIONS,)),
                          ("actions_expanded", np.uint8, (MAX_ACTIONS,))], align=True)

@@ -219,6 +219,8 @@ struct Shared {
     unsigned status;
     unsigned long long plies;
     unsigned long long ub;
+    unsigned long long stage_cycles[4];  // cycles of this slice spent in select, expand, playouts, backup (thread 0 keeps them)
+    unsigned stage_mark;        // cycle counter when the playouts of the current step began
 };
 
 // `n_steps` steps of tree g by the whole block, from the state the tree has in global memory and back to it.
@@ -264,6 +266,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             s.selected = st->selected;
             s.path_len = st->path_len;
         }
+        for (int k = 0; k < 4; k++) s.stage_cycles[k] = 0;
         // the "last step" arrays of the reference live as long as the instance: a new search starts from what the
         // previous one left in them (trees_actions_expanded keeps stale entries in the thrifty layout)
         s.out_neg = st->out_neg;
@@ -282,6 +285,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
     for (int step = 0; step < n_steps; step++) {
         // =========================================================== select + expand (warp 0)
         if (warp == 0) {
+            const unsigned c_step = (unsigned)clock();   // 32-bit cycle counts: differences are right modulo 2^32
             int node = 0;
             int4 r = rec[0];
             int depth = 0;
@@ -333,6 +337,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 }
             }
             // ------------------------------------------------------- expand (_expand_1_* and _expand_2_*)
+            const unsigned c_expand = (unsigned)clock();
             const int sel_turn = meta_turn(r.w);
             int mode, n_exp = 0, exp_mask = 0, first_child = -1, pick = 0, n_slots = 0;
             if (r.w & META_TERMINAL) {
@@ -454,6 +459,10 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 s.selected = node;
                 s.sel_meta = r.w;
                 s.path_len = depth + 1;
+                const unsigned c_play = (unsigned)clock();
+                s.stage_cycles[0] += c_expand - c_step;
+                s.stage_cycles[1] += c_play - c_expand;
+                s.stage_mark = c_play;
             }
         }
         __syncthreads();
@@ -575,6 +584,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
 
         // =========================================================== backup (warp 0)
         if (warp == 0) {
+            const unsigned c_backup = (unsigned)clock();
             const int mode = s.mode;
             const int n_exp = s.n_exp;
             const int sel_meta = s.sel_meta;
@@ -636,6 +646,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             if (lane == 0) {
                 s.out_neg = neg_tot;
                 s.out_pos = pos_tot;
+                s.stage_cycles[2] += c_backup - s.stage_mark;
+                s.stage_cycles[3] += (unsigned)clock() - c_backup;
             }
             __syncwarp();
         }
@@ -659,6 +671,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         st->status = s.status;
         st->plies = s.plies;
         st->ub_draws = s.ub;
+        for (int k = 0; k < 4; k++) st->stage_ms[k] = (first ? 0.f : st->stage_ms[k]) + (float)s.stage_cycles[k] * p.ms_per_cycle;
         for (int a = 0; a < A; a++) {
             p.child_out[(g * A + a) * 2 + 0] = s.child_out[a][0];
             p.child_out[(g * A + a) * 2 + 1] = s.child_out[a][1];

@@ -60,6 +60,10 @@ struct TreeState {
     unsigned long long plies;
     unsigned long long ub_draws;
     float us_per_step;   // work queue: smoothed time per step of the tree's slices in the current launch (microseconds)
+    // time this tree's block spent in the four stages of its steps since the search began, in milliseconds at the nominal
+    // SM clock (cycle counter of the SM the block ran on): select, expand, playouts, backup.  The reference times the same
+    // stages with host clocks around its launches (src/mctsnc.py:606-686).
+    float stage_ms[4];
     int reserved;
 };
 
@@ -199,6 +203,7 @@ struct SearchParams {
     long long *trace;
     int *trace_count;
     int trace_cap;
+    float ms_per_cycle;      // 1 / (nominal SM clock in kHz): converts cycle counts into the stage times of TreeState
 };
 
 }  // namespace mctsnc

@@ -72,9 +72,11 @@ struct Params {
     int n_trees;
     int n_playouts;
     int variant;
+    int tree_base;            // a launch works on the trees [tree_base, tree_base + its number of trees)
     int first;                // 1: reset the trees to the roots before anything else
     int backup_only;          // 1: only the backup of the pending step
     float ucb_c;
+    float ms_per_cycle;       // 1 / (nominal SM clock in kHz), for the stage times of TreeState
 };
 
 __device__ __forceinline__ unsigned bitrev8(unsigned x) { return __brev(x) >> 24; }
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
     __shared__ int4 s_rec;
     __shared__ int s_node;
     __shared__ int s_pick;
-    const int g = blockIdx.x;
+    const int g = p.tree_base + (int)blockIdx.x;
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int P = p.n_playouts;
@@ -174,11 +176,13 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
             st->status = 0;
             st->plies = 0;
             st->ub_draws = 0;
+            for (int k = 0; k < 4; k++) st->stage_ms[k] = 0.f;
             si->pending = 0;
         }
         __syncthreads();
     }
     const int root_turn = g_turn(rec[0].w);
+    const unsigned c_begin = (unsigned)clock();   // stage times: cycle counts of thread 0 (differences modulo 2^32)
 
     // =============================================================== backup of the step whose playouts have finished
     if (si->pending) {
@@ -252,6 +256,8 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
         __threadfence_block();
         __syncthreads();
     }
+    const unsigned c_select = (unsigned)clock();
+    if (tid == 0) st->stage_ms[3] += (float)(c_select - c_begin) * p.ms_per_cycle;
     if (p.backup_only) return;
 
     // =============================================================== select
@@ -321,6 +327,7 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
     }
 
     // =============================================================== expand
+    const unsigned c_expand = (unsigned)clock();
     const int4 r = s_rec;
     const int node = s_node;
     const int sel_turn = g_turn(r.w);
@@ -443,6 +450,8 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
         si->pending = 1;
         st->selected = node;
         st->path_len = depth + 1;
+        st->stage_ms[0] += (float)(c_expand - c_select) * p.ms_per_cycle;
+        st->stage_ms[1] += (float)((unsigned)clock() - c_expand) * p.ms_per_cycle;
     }
 }
 
@@ -574,7 +583,7 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
     unsigned *my = s_mem + tid;                                                     // word k of this thread: my[k * DYN_THREADS]
     unsigned *tpl = s_mem + THREAD_WORDS * DYN_THREADS + warp * THREAD_WORDS;       // this warp's parent template
     unsigned char *tpl_bytes = reinterpret_cast<unsigned char *>(tpl);
-    int tree = (int)(((long long)blockIdx.x * (DYN_THREADS / 32) + warp) % total_trees);
+    int tree = p.tree_base + (int)(((long long)blockIdx.x * (DYN_THREADS / 32) + warp) % total_trees);
     int tried = 0;
     bool have_tpl = false, exhausted = false;
     // warp-uniform description of the current tree's step
@@ -689,7 +698,7 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
         if (exhausted && __ballot_sync(0xFFFFFFFFu, playing) == 0u) {
             // ---- this tree's games are all taken and this warp's are finished: next tree
             if (++tried >= total_trees) break;
-            tree = tree + 1 == total_trees ? 0 : tree + 1;
+            tree = tree + 1 == p.tree_base + total_trees ? p.tree_base : tree + 1;
             have_tpl = false;
             continue;
         }

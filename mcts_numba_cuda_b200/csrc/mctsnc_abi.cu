@@ -23,6 +23,7 @@ using namespace mctsnc;
 namespace {
 
 constexpr int MAX_TREE_DEPTH = 2048;  // src/mctsnc.py:197
+constexpr int GOMOKU_STREAMS = 8;     // tree groups of a Gomoku search launch that run out of step with each other
 
 #define CUDA_TRY(expr)                        \
     do {                                      \
@@ -51,6 +52,7 @@ struct DevResult {
     int max_size;
     long long total_nodes;
     long long depth_sum;
+    float stage_ms[4];   // mean over the search's trees of TreeState::stage_ms
 };
 
 }  // namespace
@@ -109,6 +111,13 @@ struct mctsnc_handle {
     bool staging_in_flight = false;
     float last_ms = 0.f;
     long long last_steps = 0;
+    // Gomoku: streams of the tree groups of a search launch, with the events that fork them from and join them to the
+    // caller's stream
+    cudaStream_t g_stream[GOMOKU_STREAMS] = {};
+    cudaEvent_t g_fork = nullptr, g_join[GOMOKU_STREAMS] = {};
+    float ms_per_cycle = 0.f;  // 1 / nominal SM clock in kHz
+    cudaEvent_t ev_r0 = nullptr, ev_r1 = nullptr;  // behind the two reduction kernels of mctsnc_run
+    float reduce_ms[2] = {0.f, 0.f};
     int staged_roots = 0;  // roots resident on the device from the last staging
     size_t dyn_smem = 0;   // dynamic shared memory of the search kernel: the tree's random streams
 };
@@ -237,6 +246,11 @@ __global__ void reduce_over_trees_kernel(const int4 *rec, const TreeState *state
         d.n_root_actions = __popc(mask0);
         d.max_depth = sh_maxd[0];
         d.depth_sum = sh_depth[0];
+        for (int k = 0; k < 4; k++) {
+            float acc = 0.f;
+            for (int t = 0; t < n_trees; t++) acc += state[b * n_trees + t].stage_ms[k];
+            d.stage_ms[k] = acc / (float)n_trees;
+        }
         dres[b] = d;
     }
 }
@@ -396,6 +410,11 @@ __global__ void gomoku_reduce_over_trees_kernel(const int4 *rec, const unsigned 
         d.n_root_actions = n_children0;
         d.max_depth = sh_maxd[0];
         d.depth_sum = sh_depth[0];
+        for (int k = 0; k < 4; k++) {
+            float acc = 0.f;
+            for (int t = 0; t < n_trees; t++) acc += state[b * n_trees + t].stage_ms[k];
+            d.stage_ms[k] = acc / (float)n_trees;
+        }
         dres[b] = d;
     }
 }
@@ -514,6 +533,13 @@ void release(mctsnc_handle *h) {
     if (h->ev0) cudaEventDestroy(h->ev0);
     if (h->ev1) cudaEventDestroy(h->ev1);
     if (h->ev_staged) cudaEventDestroy(h->ev_staged);
+    if (h->ev_r0) cudaEventDestroy(h->ev_r0);
+    if (h->ev_r1) cudaEventDestroy(h->ev_r1);
+    if (h->g_fork) cudaEventDestroy(h->g_fork);
+    for (int g = 0; g < GOMOKU_STREAMS; g++) {
+        if (h->g_join[g]) cudaEventDestroy(h->g_join[g]);
+        if (h->g_stream[g]) cudaStreamDestroy(h->g_stream[g]);
+    }
 }
 
 #ifndef MCTSNC_SLICE_STEPS
@@ -596,7 +622,14 @@ int stage_roots(mctsnc_handle *h, int batch, const int8_t *boards, const int8_t 
     return 0;
 }
 
-// Gomoku: two launches per step (tree step, playouts) and a closing backup, all enqueued without waiting
+// Gomoku: two launches per step (tree step, playouts) and a closing backup, all enqueued without waiting.
+//
+// The trees are split into groups, each with a stream of its own: a tree's next step only needs that tree's games to be
+// over, so the groups run out of step with each other and the lanes one tree leaves idle while its longest games finish
+// (up to ~170 plies against a mean of ~85) play the games of the others.  Every playout launch asks for enough blocks
+// for all its games at once; blocks whose warps find no game left return at once and make room for the blocks of the
+// other groups' launches, so the device is shared by whatever games exist at the moment.  No kernel waits for another:
+// the order inside a group is stream order, the groups are forked from and joined to the caller's stream with events.
 int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cudaStream_t stream) {
     gomoku::Params p;
     p.rec = h->rec;
@@ -622,25 +655,42 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
     p.n_playouts = h->cfg.n_playouts;
     p.variant = h->cfg.variant;
     p.ucb_c = h->cfg.ucb_c;
-    const unsigned trees = (unsigned)((long long)batch * h->cfg.n_trees);
+    p.ms_per_cycle = h->ms_per_cycle;
+    const int trees = (int)((long long)batch * h->cfg.n_trees);
     const bool ocp = is_ocp(h->cfg);
-    const int P = h->cfg.n_playouts;
-    // persistent playout grid: as many blocks as fit on the device at once (three per SM, limited by shared memory)
+    // resident playout blocks: three per SM (limited by shared memory)
     int per_sm = 0;
     const void *pk = ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pk, gomoku::DYN_THREADS, h->dyn_smem) != cudaSuccess || per_sm < 1) per_sm = 1;
-    const unsigned pgrid = (unsigned)(per_sm * h->sm_count);
+    const long long resident = (long long)per_sm * h->sm_count;
     h->threads = gomoku::DYN_THREADS;
     h->blocks_per_sm = per_sm;
-    (void)P;
+    const int groups = trees < GOMOKU_STREAMS ? trees : GOMOKU_STREAMS;
+    CUDA_TRY(cudaEventRecord(h->g_fork, stream));
+    for (int g = 0; g < groups; g++) CUDA_TRY(cudaStreamWaitEvent(h->g_stream[g], h->g_fork, 0));
     for (int s = 0; s <= steps; s++) {
         p.first = (first && s == 0) ? 1 : 0;
         p.backup_only = s == steps ? 1 : 0;
-        if (ocp) gomoku::tree_step_kernel<true><<<trees, 256, 0, stream>>>(p);
-        else gomoku::tree_step_kernel<false><<<trees, 256, 0, stream>>>(p);
-        if (s == steps) break;
-        if (ocp) gomoku::playout_dynamic_kernel<true><<<pgrid, gomoku::DYN_THREADS, h->dyn_smem, stream>>>(p, (int)trees);
-        else gomoku::playout_dynamic_kernel<false><<<pgrid, gomoku::DYN_THREADS, h->dyn_smem, stream>>>(p, (int)trees);
+        for (int g = 0; g < groups; g++) {
+            const int t0 = (int)((long long)trees * g / groups), t1 = (int)((long long)trees * (g + 1) / groups);
+            const int n = t1 - t0;
+            p.tree_base = t0;
+            cudaStream_t gs = h->g_stream[g];
+            if (ocp) gomoku::tree_step_kernel<true><<<n, 256, 0, gs>>>(p);
+            else gomoku::tree_step_kernel<false><<<n, 256, 0, gs>>>(p);
+            if (s == steps) continue;
+            // one lane per game of the step at most (OCP: one child per tree, ACP: up to 225), never more than fit at once
+            const long long games = (long long)n * h->cfg.n_playouts * (ocp ? 1 : h->A);
+            long long blocks = (games + gomoku::DYN_THREADS - 1) / gomoku::DYN_THREADS;
+            if (blocks > resident) blocks = resident;
+            if (blocks < 1) blocks = 1;
+            if (ocp) gomoku::playout_dynamic_kernel<true><<<(unsigned)blocks, gomoku::DYN_THREADS, h->dyn_smem, gs>>>(p, n);
+            else gomoku::playout_dynamic_kernel<false><<<(unsigned)blocks, gomoku::DYN_THREADS, h->dyn_smem, gs>>>(p, n);
+        }
+    }
+    for (int g = 0; g < groups; g++) {
+        CUDA_TRY(cudaEventRecord(h->g_join[g], h->g_stream[g]));
+        CUDA_TRY(cudaStreamWaitEvent(stream, h->g_join[g], 0));
     }
     return (int)cudaGetLastError();
 }
@@ -670,6 +720,7 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
     p.steps = steps;
     p.first = first;
     p.ucb_c = h->cfg.ucb_c;
+    p.ms_per_cycle = h->ms_per_cycle;
     const long long trees = (long long)batch * h->cfg.n_trees;
     const int threads = h->cfg.threads_per_tree > 0 ? h->cfg.threads_per_tree : choose_threads(h, trees);
     h->threads = threads;
@@ -754,6 +805,15 @@ int fetch_results(mctsnc_handle *h, int batch, const long long *sums_dev, mctsnc
         r.total_nodes = d.total_nodes;
         r.depth_sum = d.depth_sum;
         r.max_size = d.max_size;
+        for (int k = 0; k < 4; k++) r.stage_ms[k] = d.stage_ms[k];
+        if (is_gomoku(h->cfg)) {
+            // the playouts of a Gomoku step run in a kernel of their own, shared by all trees: their time is what is left of
+            // the loop after the per-tree stages
+            const float rest = h->last_ms - (d.stage_ms[0] + d.stage_ms[1] + d.stage_ms[3]);
+            r.stage_ms[2] = rest > 0.f ? rest : 0.f;
+        }
+        r.reduce_ms[0] = h->reduce_ms[0];
+        r.reduce_ms[1] = h->reduce_ms[1];
         for (int a = 0; a < A; a++) {
             r.root_ns[a] = h->h_sums[(long long)b * 3 * A + a];
             r.actions_ns[a] = h->h_sums[(long long)b * 3 * A + A + a];
@@ -815,6 +875,9 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     cudaDeviceProp prop;
     CUDA_TRY(cudaGetDeviceProperties(&prop, c.device));
     h->sm_count = prop.multiProcessorCount;
+    int clock_khz = 0;
+    if (cudaDeviceGetAttribute(&clock_khz, cudaDevAttrClockRate, c.device) != cudaSuccess || clock_khz <= 0) clock_khz = 1965000;
+    h->ms_per_cycle = 1.0f / (float)clock_khz;
     h->n_trees_total = (long long)c.max_batch * c.n_trees;
     const long long nodes = h->n_trees_total * h->cfg.node_capacity;
     const bool ocp = is_ocp(c);
@@ -868,6 +931,15 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc && cudaEventCreate(&h->ev0) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && cudaEventCreate(&h->ev1) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && cudaEventCreateWithFlags(&h->ev_staged, cudaEventDisableTiming) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaEventCreate(&h->ev_r0) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && cudaEventCreate(&h->ev_r1) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+    if (!rc && is_gomoku(c)) {
+        if (cudaEventCreateWithFlags(&h->g_fork, cudaEventDisableTiming) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
+        for (int g = 0; g < GOMOKU_STREAMS && !rc; g++)
+            if (cudaStreamCreateWithFlags(&h->g_stream[g], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&h->g_join[g], cudaEventDisableTiming) != cudaSuccess)
+                rc = MCTSNC_E_NO_MEMORY;
+    }
     if (!rc) rc = (int)cudaMemset(h->state, 0, sizeof(TreeState) * h->n_trees_total);
     if (!rc) rc = (int)cudaMemset(h->actions_expanded, 0, sizeof(short) * h->n_trees_total * (h->A + 2));
     if (!rc) rc = (int)cudaMemset(h->child_out, 0, sizeof(int) * h->n_trees_total * h->A * 2);
@@ -966,8 +1038,13 @@ extern "C" int mctsnc_run(mctsnc_handle *h, const int8_t *board, const int8_t *e
     h->last_steps = done;
     rc = launch_reduce_trees(h, 1, h->sums, 0);
     if (rc) return rc;
+    CUDA_TRY(cudaEventRecord(h->ev_r0, 0));
     rc = launch_reduce_actions(h, 1, h->sums, 0);
     if (rc) return rc;
+    CUDA_TRY(cudaEventRecord(h->ev_r1, 0));
+    CUDA_TRY(cudaEventSynchronize(h->ev_r1));
+    CUDA_TRY(cudaEventElapsedTime(&h->reduce_ms[0], h->ev1, h->ev_r0));
+    CUDA_TRY(cudaEventElapsedTime(&h->reduce_ms[1], h->ev_r0, h->ev_r1));
     return fetch_results(h, 1, h->sums, out, 0);
 }
 
@@ -1433,6 +1510,7 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
     p.trace = nullptr;
     p.trace_count = nullptr;
     p.trace_cap = 0;
+    p.ms_per_cycle = 0.f;
     const size_t dyn_smem = sizeof(ulonglong2) * (size_t)per_tree;   // <= 28 KB: below the 48 KB that need an opt-in
     if (ocp) c4::search_kernel<true><<<n_trees, 256, dyn_smem, s>>>(p);
     else c4::search_kernel<false><<<n_trees, 256, dyn_smem, s>>>(p);

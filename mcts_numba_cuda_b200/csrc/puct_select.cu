@@ -33,6 +33,10 @@ enum Reason {
     R_INVALID_CHILD_OOB = 15, R_INVALID_UNKNOWN = 16
 };
 constexpr int MAX_EVALUATIONS = 2;
+#ifndef PUCT_SELECT_WARPS_PER_BLOCK
+#define PUCT_SELECT_WARPS_PER_BLOCK 2
+#endif
+constexpr int SELECT_WARPS_PER_BLOCK = PUCT_SELECT_WARPS_PER_BLOCK;  // traversals per thread block of the select kernel
 constexpr float LOWEST = -3.4028234663852886e38f;
 constexpr int NO_EDGE = 0x7FFFFFFF;
 
@@ -95,12 +99,18 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
                               const int *__restrict__ node_expanded, const int *__restrict__ tree_nodes, int *out_selected_node,
                               int *out_path_eids, int *out_path_len, int trees, int nodes, int edges, int warps,
                               int path_depth, int virtual_loss) {
-    const int tree = blockIdx.x;
+    // Traversal i = tree * warps + w is run by warp i of the grid, in blocks of SELECT_WARPS_PER_BLOCK warps.  The reference
+    // puts the `warps` traversals of a tree into one block (src/puct/puct_gpu_v3_cpp.cu:472-473); with 8 traversals per
+    // tree most of them lose the claim at the root and leave after two evaluations, and a block of 8 warps then keeps
+    // its 6 idle warp slots until its last traversal has gone all the way down.  Small blocks give the slots back at
+    // once; the traversals of a tree still start together (their warps are neighbours in the grid).
     const int lane = threadIdx.x & 31;
-    const int wid = threadIdx.x >> 5;
+    const int traversal = blockIdx.x * (int)(blockDim.x >> 5) + (int)(threadIdx.x >> 5);
+    const int tree = traversal / warps;
+    const int wid = traversal - tree * warps;
     const int vl = VL_GENERAL ? virtual_loss : 1;
-    if (tree >= trees || wid >= min((int)(blockDim.x >> 5), warps)) return;
-    const int out_ix = tree * warps + wid;
+    if (tree >= trees) return;
+    const int out_ix = traversal;
     int *path = out_path_eids + (long long)out_ix * path_depth;
     const int node_cnt = tree_nodes[tree];
     if (!(path_depth >= 1 && nodes > 0 && node_cnt > 0 && node_cnt <= nodes && node_cnt <= NODE_LIMIT && edges > 0 &&
@@ -323,11 +333,13 @@ static int launch_select(float cpuct, float c_pw, float alpha_pw, int soft_winne
                          int *node_expand_inflight, const int *node_expanded, const int *tree_nodes, int *out_selected_node,
                          int *out_path_eids, int *out_path_len, int trees, int nodes, int edges, int warps, int path_depth,
                          cudaStream_t stream) {
+    const long long traversals = (long long)trees * warps;
+    const unsigned grid = (unsigned)((traversals + SELECT_WARPS_PER_BLOCK - 1) / SELECT_WARPS_PER_BLOCK);
 #define PUCT_LAUNCH(E)                                                                                                      \
-    select_kernel<VL, E><<<trees, warps * 32, 0, stream>>>(cpuct, c_pw, alpha_pw, soft_winner, edge_child_id, edge_prior,  \
-                                                          edge_W, edge_N, edge_inflight, node_expand_inflight,             \
-                                                          node_expanded, tree_nodes, out_selected_node, out_path_eids,     \
-                                                          out_path_len, trees, nodes, edges, warps, path_depth, virtual_loss)
+    select_kernel<VL, E><<<grid, SELECT_WARPS_PER_BLOCK * 32, 0, stream>>>(                                                 \
+        cpuct, c_pw, alpha_pw, soft_winner, edge_child_id, edge_prior, edge_W, edge_N, edge_inflight, node_expand_inflight, \
+        node_expanded, tree_nodes, out_selected_node, out_path_eids, out_path_len, trees, nodes, edges, warps, path_depth,  \
+        virtual_loss)
     if (edges <= 32) PUCT_LAUNCH(1);
     else if (edges <= 64) PUCT_LAUNCH(2);
     else if (edges <= 128) PUCT_LAUNCH(4);

@@ -312,7 +312,8 @@ class MCTSNC:
             "actions_expanded": np.array(res.actions_expanded[:A], dtype=bool),
             "playouts": int(res.playouts), "plies": int(res.plies), "ub_draws": int(res.ub_draws), "status": int(res.status),
             "max_depth": int(res.max_depth), "total_nodes": int(res.total_nodes), "depth_sum": int(res.depth_sum),
-            "max_size": int(res.max_size), "device_ms": float(res.device_ms)}
+            "max_size": int(res.max_size), "device_ms": float(res.device_ms),
+            "stage_ms": [float(x) for x in res.stage_ms], "reduce_ms": [float(x) for x in res.reduce_ms]}
         self.best_action = np.int16(res.best_action)
         self.best_win_flag = bool(res.best_win_flag)
         self.best_n = np.int64(res.best_n)
@@ -322,11 +323,13 @@ class MCTSNC:
         self.status = int(res.status)
         self.ub_draws = int(res.ub_draws)
         self.device_time = float(res.device_ms) * 1e-3
-        # the loop runs on the device in one piece: its CUDA-event time is the loop time; the per-stage split of the
-        # reference (host clocks around each launch, src/mctsnc.py:606-686) has no counterpart
+        # The loop runs on the device in one piece: its CUDA-event time is the loop time.  The per-stage times of the
+        # reference (host clocks around each launch, src/mctsnc.py:606-686) are here the time a tree's thread block spent in
+        # each stage, counted on the device (mean over the trees, which run side by side); the two reductions are timed
+        # with CUDA events.
         self.time_loop = self.device_time
-        self.time_select = self.time_expand = self.time_playout = self.time_backup = float("nan")
-        self.time_reduce_over_trees = self.time_reduce_over_actions = float("nan")
+        self.time_select, self.time_expand, self.time_playout, self.time_backup = (1e-3 * float(x) for x in res.stage_ms)
+        self.time_reduce_over_trees, self.time_reduce_over_actions = (1e-3 * float(x) for x in res.reduce_ms)
 
     def _make_actions_info(self):
         """``actions_info`` with the keys of ``src/mctsnc.py:496-563`` (one layout for thrifty and prodigal: keyed by action)."""

@@ -103,6 +103,22 @@ def test_info_dicts_have_the_reference_keys(capsys):
                                        "mean_expand", "mean_playout", "mean_backup"}
     assert set(perf["trees"]) == {"count", "mean_depth", "max_depth", "mean_size", "max_size"}
     assert perf["playouts"] == int(e["n_root"]) and perf["steps"] == 50
+    # every time is a number (the reference fills them all, src/mctsnc.py:448-494), the four stages add up to the loop
+    times = perf["times_[ms]"]
+    assert all(np.isfinite(v) and v >= 0 for v in times.values()), times
+    stages = times["mean_select"] + times["mean_expand"] + times["mean_playout"] + times["mean_backup"]
+    assert 0.5 * times["mean_loop"] <= stages <= 1.1 * times["mean_loop"], times
+    assert times["reduce_over_trees"] > 0 and times["reduce_over_actions"] > 0
+
+
+def test_stage_times_of_a_gomoku_search_are_filled():
+    ai = MCTSNC((15, 15), 0, 225, search_time_limit=np.inf, search_steps_limit=6, n_trees=2, n_playouts=32, device_memory=16.0,
+                verbose_info=False)
+    ai.init_device_side_arrays()
+    ai.run(np.zeros((15, 15), np.int8), None, 1)
+    times = ai.performance_info["times_[ms]"]
+    assert all(np.isfinite(v) and v >= 0 for v in times.values()), times
+    assert times["mean_playout"] > times["mean_select"] > 0 and times["mean_expand"] > 0 and times["mean_backup"] > 0
 
 
 def test_json_dump_has_the_reference_keys(tmp_path):
