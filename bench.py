@@ -657,13 +657,14 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    ev[0].record()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
     for k in range(args.steps):
         searcher.search_async(None, None, None, args.search_steps, reseed=True)
-        ev[k + 1].record()
+    searcher.drain()      # the exchange of the last pass (all-reduce + argmax) is part of the timed region
+    ev1.record()
     barrier()
-    dev_ms = ev[0].elapsed_time(ev[-1])
+    dev_ms = ev0.elapsed_time(ev1)
     res = searcher.fetch(B)
     local_playouts = int(res["playouts"].sum())   # this rank's trees
     local_plies = int(res["plies"].sum())

@@ -142,6 +142,15 @@ int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *bo
 int mctsnc_finish_batch_device(mctsnc_handle *h, int32_t batch, const int64_t *summed_device, mctsnc_result *results,
                                void *stream);
 
+/* mctsnc_search_batch_device in its two parts, for callers that overlap the exchange of one batch with the search of the
+   next: launch stages the roots (or reuses the resident ones), re-seeds and runs the searches; reduce_trees forms the
+   partial sums (_reduce_over_trees_*, src/mctsnc.py:2223-2296).  reduce_trees and finish share per-handle buffers (win
+   flags, statistics): the caller orders reduce_trees of a batch after the finish of the batch before (an event), the
+   searches themselves need no such wait. */
+int mctsnc_launch_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards_host, const int8_t *extra_infos_host,
+                               const int8_t *turns_host, int64_t steps, int32_t reseed, void *stream);
+int mctsnc_reduce_trees_device(mctsnc_handle *h, int32_t batch, int64_t *partial_sums_device, void *stream);
+
 /* Replaces the copy_to_host calls of _json_dump (src/mctsnc.py:2393-2438): converts the trees of search `search`
    (0 for run()) into the reference's array formats.  dst holds n_trees * max_nodes * <row> elements; rows at or
    beyond a tree's size are filled with 0 (-1 for "trees").  */

@@ -44,6 +44,26 @@ int puct_backup_launch(int virtual_loss, float *edge_W, int *edge_N, int *edge_i
                        const int *tree_nodes, const int *out_selected_node, const int *out_path_eids, const int *out_path_len,
                        const float *path_edge_values, int trees, int nodes, int edges, int warps, int path_depth, void *stream);
 
+/* Replaces the two older select kernels of the reference, for trees that keep virtual visits per child NODE
+   (node_inflight: int32[trees][nodes]) instead of per edge:
+     variant 0 (preclaim)     _select_kernel_native,        src/puct/puct_gpu_v2.py:573-697
+     variant 1 (counter-CAS)  _select_kernel_winner_recalc, src/puct/puct_gpu_v2.py:700-840
+   The reference launches them from Python as kernel[trees, warps * 32](cpuct, c_pw, alpha_pw, arrays...) with the shapes
+   taken from the arrays (src/puct/test_puct_gpu_v2.py:320-354); here the shapes are arguments, as in the v3 launcher.
+   Results: (kind << 22) | (slot << 14) | node with kinds INVALID 0, EXPAND 1, TERMINAL 2, DEPTH_LIMIT 3 (no reason bits,
+   no BUSY kind); path entries (parent << 8) | slot; a failed traversal gives back every visit it made. */
+int puct_v2_select_launch(int variant, float cpuct, float c_pw, float alpha_pw, const int *edge_child_id, const float *edge_prior,
+                          const float *edge_W, const int *edge_N, int *node_inflight, int *node_expand_inflight,
+                          const int *node_expanded, const int *tree_nodes, int *out_selected_node, int *out_path_eids,
+                          int *out_path_len, int trees, int nodes, int edges, int warps, int path_depth, void *stream);
+
+/* Replaces _backup_kernel_native, src/puct/puct_gpu_v2.py:847-927 (per-node layout): per path edge the child's visits
+   -= virtual_loss, N += 1, W += value; an EXPAND result returns its ticket.  path_edge_values == NULL releases only. */
+int puct_v2_backup_launch(int virtual_loss, const int *edge_child_id, float *edge_W, int *edge_N, int *node_inflight,
+                          int *node_expand_inflight, const int *tree_nodes, const int *out_selected_node, const int *out_path_eids,
+                          const int *out_path_len, const float *path_edge_values, int trees, int nodes, int edges, int warps,
+                          int path_depth, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,11 +21,12 @@ E_BAD_ARGUMENT, E_UNSUPPORTED, E_NO_MEMORY, E_BAD_ROOT, E_CAPACITY, E_NO_DEVICE 
 
 # symbols declared in include/mctsnc_b200.h; the CPU test-suite checks that the library exports every one of them
 EXPORTED = ["mctsnc_create", "mctsnc_destroy", "mctsnc_reset_rng", "mctsnc_run", "mctsnc_run_batch",
-            "mctsnc_search_batch_device", "mctsnc_finish_batch_device", "mctsnc_export", "mctsnc_export_rng",
+            "mctsnc_search_batch_device", "mctsnc_finish_batch_device", "mctsnc_launch_batch_device",
+            "mctsnc_reduce_trees_device", "mctsnc_export", "mctsnc_export_rng",
             "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_trace_slices", "mctsnc_read_slices", "mctsnc_error_string"]
 # the PUCT entry points keep the names of the reference's native library (include/puct_b200.h)
 EXPORTED_PUCT = ["puct_select_winner_recalc_launch", "puct_select_virtual_loss_launch", "puct_backup_launch",
-                 "puct_cpp_cuda_error_string"]
+                 "puct_cpp_cuda_error_string", "puct_v2_select_launch", "puct_v2_backup_launch"]
 # decoupled-UCT select for simultaneous moves: no counterpart in the reference (include/duct_b200.h)
 EXPORTED_DUCT = ["duct_select_launch", "duct_backup_launch"]
 
@@ -87,6 +88,8 @@ def lib():
         L.mctsnc_run_batch.argtypes = [vp, i32, vp, vp, vp, i64, i32, vp]
         L.mctsnc_search_batch_device.argtypes = [vp, i32, vp, vp, vp, i64, i32, vp, vp]
         L.mctsnc_finish_batch_device.argtypes = [vp, i32, vp, vp, vp]
+        L.mctsnc_launch_batch_device.argtypes = [vp, i32, vp, vp, vp, i64, i32, vp]
+        L.mctsnc_reduce_trees_device.argtypes = [vp, i32, vp, vp]
         L.mctsnc_export.argtypes = [vp, i32, i32, vp, i64]
         L.mctsnc_export_rng.argtypes = [vp, i32, i32, vp, i64]
         L.mctsnc_query.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i64)]

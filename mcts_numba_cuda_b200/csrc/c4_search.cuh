@@ -197,8 +197,8 @@ struct Shared {
     int child_slot[A];       // and its slot (-1: no playouts: terminal, or not picked in OCP)
     int child_out[A][2];     // trees_playout_outcomes_children (persists over steps)
     short ae[A + 2];         // trees_actions_expanded row (persists over steps)
-    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the seven bits of the column
-    // (0x7F << 7 * column) in bits 0..48 and the column's bit in bits 54..60, i.e. where it sits in the pre-shifted column
+    // move_lut[set * 8 + ord]: for the ord-th column (ascending) of the column set `set`, the six cells of the column
+    // (0x3F << 7 * column) in bits 0..47 and the column's bit in bits 54..60, i.e. where it sits in the pre-shifted column
     // set the playout loop keeps (GameSlot::legal), moved up by 48.  An ordinal the set does not have (only a uniform
     // draw of exactly 1.0f gives one: ord == number of columns) maps to MOVE_LUT_NO_COLUMN: no cell, bit 63 set.
     unsigned long long move_lut[128 * 8];
@@ -476,8 +476,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         // The board of a game in progress is three words: the stones of the side that moves at the even plies of a
         // block of PLIES_PER_CHECK plies (a game starts at ply 0 of a block, so that is the side to move in the game's
         // first position), the stones of the other side, and `top`, one bit per column at its lowest empty cell (the
-        // guard bit once the column is full; top = all stones + BOTTOM_ROW).  A move in column c is then
-        // top & (seven bits of column c), and top + move puts the marker one cell up.
+        // guard bit once the column is full; top = all stones + BOTTOM_ROW).  A move in a column with room is then
+        // top & (six cells of the column), and top + move puts the marker one cell up.
         {
             const int n_items = s.n_slots << p.log2_playouts;
             // the side to move in the played-out positions: the other side than at the selected node, unless the
@@ -704,7 +704,7 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
                 seen++;
             }
         s.move_lut[i] = col < 0 ? MOVE_LUT_NO_COLUMN
-                                : (0x7FULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
+                                : (0x3FULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
     }
     const bool queued = p.queue != nullptr;
     for (;;) {

@@ -557,6 +557,11 @@ __device__ __noinline__ EmuResult playout_emulated(const unsigned *start /* 16 w
 // swap-remove leaves them, src/mctsnc_game_mechanics.py:209-217), 15 words hold the board rows (low half: stones of
 // -1, high half: stones of +1).
 constexpr int LIST_WORDS = 57, ROW_WORDS = 15, THREAD_WORDS = LIST_WORDS + ROW_WORDS;
+// Tables of the exactly-five test, behind the per-thread and per-warp words of the block's shared memory:
+// FIVE_WORDS words = one bit per 11-cell window (the new stone in the middle, five cells either way; bit k of the index =
+// the mover's stone k - 5 cells along the line): set iff the stones next to the middle add up to exactly 4;
+// then per board row two masks of the window cells that exist for the lines that cross rows.
+constexpr int FIVE_WORDS = 2048 / 32, TABLE_WORDS = FIVE_WORDS + 2 * M;
 
 __device__ __forceinline__ int turn_at_start(int mode, int sel_turn) { return mode == MODE_TREE_FULL ? sel_turn : -sel_turn; }
 
@@ -583,14 +588,35 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
     unsigned *my = s_mem + tid;                                                     // word k of this thread: my[k * DYN_THREADS]
     unsigned *tpl = s_mem + THREAD_WORDS * DYN_THREADS + warp * THREAD_WORDS;       // this warp's parent template
     unsigned char *tpl_bytes = reinterpret_cast<unsigned char *>(tpl);
+    unsigned *s_five = s_mem + THREAD_WORDS * (DYN_THREADS + DYN_THREADS / 32);      // FIVE_WORDS words
+    uint2 *s_rows = reinterpret_cast<uint2 *>(s_five + FIVE_WORDS);                 // M pairs of window masks
+    for (int wd = tid; wd < FIVE_WORDS; wd += DYN_THREADS) {
+        unsigned bits = 0;
+        for (int b = 0; b < 32; b++) {
+            const unsigned window = (unsigned)(wd * 32 + b);
+            int above = 0, below = 0;
+            while (above < 5 && ((window >> (6 + above)) & 1u)) above++;
+            while (below < 5 && ((window >> (4 - below)) & 1u)) below++;
+            if (above + below == 4) bits |= 1u << b;
+        }
+        s_five[wd] = bits;
+    }
+    if (tid < M) {
+        // window cell 5 + k is the cell k rows down the line for the vertical and the diagonal, k rows UP for the
+        // anti-diagonal (whose cells are gathered the other way round); cells on rows outside the board do not exist
+        const int up = tid < 5 ? tid : 5, dn = M - 1 - tid < 5 ? M - 1 - tid : 5;
+        const unsigned span = (1u << (up + dn + 1)) - 1u;
+        s_rows[tid] = make_uint2(span << (15 - up), span << (15 - dn));
+    }
+    __syncthreads();
     int tree = p.tree_base + (int)(((long long)blockIdx.x * (DYN_THREADS / 32) + warp) % total_trees);
     int tried = 0;
     bool have_tpl = false, exhausted = false;
     // warp-uniform description of the current tree's step
     int n_items = 0, mode = 0, sel_turn = 0, count0 = 0, first_child = 0, selected = 0;
-    // per-lane game
+    // per-lane game (a lane may still be playing a game of an earlier tree after the warp has moved on)
     bool playing = false;
-    int count = 0, turn = 0, action = 0, node = 0;
+    int count = 0, turn = 0, action = 0, node = 0, my_tree = 0, my_start_turn = 0;
     long long rng_idx = 0;
     unsigned long long s0 = 0, s1 = 0, start0 = 0, start1 = 0;
     unsigned plies = 0;
@@ -687,6 +713,8 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                     prev = next;
                 }
                 for (int i = 0; i < M; i++) my[(LIST_WORDS + i) * DYN_THREADS] = tpl[LIST_WORDS + i] | ((unsigned)i == stone_row ? stone_bit : 0u);
+                my_tree = tree;
+                my_start_turn = turn;
                 rng_idx = OCP ? ((long long)tree * P + t) : (((long long)tree * A + action) * P + t);
                 const ulonglong2 rs = p.rng_playout[rng_idx];
                 s0 = start0 = rs.x;
@@ -695,12 +723,17 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 playing = true;
             }
         }
-        if (exhausted && __ballot_sync(0xFFFFFFFFu, playing) == 0u) {
-            // ---- this tree's games are all taken and this warp's are finished: next tree
-            if (++tried >= total_trees) break;
-            tree = tree + 1 == p.tree_base + total_trees ? p.tree_base : tree + 1;
-            have_tpl = false;
-            continue;
+        if (exhausted) {
+            // ---- this tree's games are all taken: idle lanes take games of the next tree from now on, while the others
+            // finish what they are playing (a game carries its tree with it); after the last tree the warp plays on until
+            // its lanes are done
+            if (tried + 1 < total_trees) {
+                tried++;
+                tree = tree + 1 == p.tree_base + total_trees ? p.tree_base : tree + 1;
+                have_tpl = false;
+                continue;
+            }
+            if (__ballot_sync(0xFFFFFFFFu, playing) == 0u) break;
         }
         if (playing) {
             // ---- one ply
@@ -710,13 +743,12 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
             int outcome = 2;
             if (ord >= count) {
                 // u == 1.0f: replay this game through the byte-level emulation of the reference
-                const EmuResult er = playout_emulated(p.board + ((long long)tree * p.cap + node) * 16, turn_at_start(mode, sel_turn),
-                                                      start0, start1);
+                const EmuResult er = playout_emulated(p.board + ((long long)my_tree * p.cap + node) * 16, my_start_turn, start0, start1);
                 s0 = er.s0;
                 s1 = er.s1;
                 outcome = er.outcome;
                 plies = er.plies;
-                TreeState *st = p.state + tree;
+                TreeState *st = p.state + my_tree;
                 atomicAdd(&st->ub_draws, (unsigned long long)er.ub);
                 atomicOr(&st->status, STATUS_UB_DRAW | (er.err ? STATUS_INTERNAL : 0u));
             } else {
@@ -738,12 +770,13 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 plies++;
                 // compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) without data-dependent loops: for each of the
                 // four directions the mover's stones on the line through (i, j) are gathered into a window with the new
-                // stone at bit 15 and the cell r steps "down" the line at bit 15 + r (15 - r for the anti-diagonal), five
-                // cells either way for the directions that cross rows; the runs next to bit 15 are then counted with
-                // find-first-set / count-leading-zeros.  The reference counts at most 5 stones either way and wants a total of
-                // exactly 4, which holds iff the two runs add up to 4.  Rows outside the board are not masked when they are
-                // read (the words fetched in their place are this thread's own list words, or row 14 again): a run is cut
-                // to the number of rows that exist on its side instead.
+                // stone at bit 15 and the cell r steps down the line at bit 15 + r (15 - r for the anti-diagonal), five cells
+                // either way; a table with one bit per window then says whether the stones next to bit 15 add up to exactly
+                // 4, which is what the reference asks for (it counts at most 5 stones either way and wants a total of 4).
+                // The row words of the five rows above and below are rotated so that column j sits at bit 15: the vertical
+                // line takes bit 15 of each, the two diagonals bits 15 - r and 15 + r, which are collected for the rows above
+                // (x) and below (y) separately and sorted into the two windows afterwards.  Rows outside the board are read
+                // all the same (this thread's list words, or row 14 again) and masked out of the windows.
                 bool win;
                 {
                     const unsigned *my_row = my + (LIST_WORDS + i) * DYN_THREADS;
@@ -752,32 +785,29 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                     // bits never wrap around
                     const unsigned half = 0x7FFFu << hs;
                     const int rot = (17 + j + hs) & 31;
-                    unsigned gh = __funnelshift_r(row & half, row & half, rot);
-                    unsigned gv = 0, gd = 0, ga = 0;
+                    const unsigned gh = __funnelshift_r(row & half, row & half, rot);
+                    unsigned gv = 0, x = 0, y = 0;
 #pragma unroll
                     for (int r = 1; r <= 5; r++) {
-                        // r rows up: row i - r
-                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;
+                        const unsigned both = (1u << (15 - r)) | (1u << (15 + r));
+                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;                      // row i - r
                         const unsigned up = __funnelshift_r(up_w, up_w, rot);
                         gv |= (up >> r) & (1u << (15 - r));
-                        gd |= up & (1u << (15 - r));          // (i - r, j - r)
-                        ga |= up & (1u << (15 + r));          // (i - r, j + r)
-                        // r rows down: row i + r (row 14 again beyond the board; the run is cut below)
-                        const int rd = min(i + r, M - 1);
+                        x |= up & both;                                                            // (i - r, j - r), (i - r, j + r)
+                        const int rd = min(i + r, M - 1);                                          // row i + r
                         const unsigned dn_w = my[(LIST_WORDS + rd) * DYN_THREADS] & half;
                         const unsigned dn = __funnelshift_r(dn_w, dn_w, rot);
                         gv |= (dn << r) & (1u << (15 + r));
-                        gd |= dn & (1u << (15 + r));          // (i + r, j + r)
-                        ga |= dn & (1u << (15 - r));          // (i + r, j - r)
+                        y |= dn & both;                                                            // (i + r, j + r), (i + r, j - r)
                     }
-                    const int rows_up = i, rows_dn = M - 1 - i;
-                    // stones next to bit 15: towards higher bits (trailing ones of g >> 16), towards lower bits (leading ones
-                    // of g << 17)
-                    const int h_hi = __ffs(~(gh >> 16)) - 1, h_lo = __clz(~(gh << 17));
-                    const int v_hi = min(__ffs(~(gv >> 16)) - 1, rows_dn), v_lo = min(__clz(~(gv << 17)), rows_up);
-                    const int d_hi = min(__ffs(~(gd >> 16)) - 1, rows_dn), d_lo = min(__clz(~(gd << 17)), rows_up);
-                    const int a_hi = min(__ffs(~(ga >> 16)) - 1, rows_up), a_lo = min(__clz(~(ga << 17)), rows_dn);
-                    win = (h_hi + h_lo == 4) | (v_hi + v_lo == 4) | (d_hi + d_lo == 4) | (a_hi + a_lo == 4);
+                    const uint2 exists = s_rows[i];
+                    const unsigned below15 = 0x7C00u, above15 = 0x1F0000u;                         // bits 10..14, 16..20
+                    const unsigned gd = ((x & below15) | (y & above15)) & exists.x;                // (i - r, j - r) .. (i + r, j + r)
+                    const unsigned ga = ((x & above15) | (y & below15)) & exists.y;                // (i - r, j + r) .. (i + r, j - r)
+                    gv &= exists.x;
+                    const unsigned wh = (gh >> 10) & 0x7FFu, wv = (gv >> 10) & 0x7FFu, wd = (gd >> 10) & 0x7FFu, wa = (ga >> 10) & 0x7FFu;
+                    win = (((s_five[wh >> 5] >> (wh & 31)) | (s_five[wv >> 5] >> (wv & 31)) | (s_five[wd >> 5] >> (wd & 31)) |
+                            (s_five[wa >> 5] >> (wa & 31))) & 1u) != 0;
                 }
                 if (win) outcome = turn;
                 else if (count == 0) outcome = 0;
@@ -785,8 +815,8 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
             }
             if (outcome != 2) {
                 p.rng_playout[rng_idx] = make_ulonglong2(s0, s1);
-                if (outcome != 0) atomicAdd(&p.child_out[(tree * A + action) * 2 + (outcome > 0 ? 1 : 0)], 1);
-                atomicAdd(&p.state[tree].plies, (unsigned long long)plies);
+                if (outcome != 0) atomicAdd(&p.child_out[(my_tree * A + action) * 2 + (outcome > 0 ? 1 : 0)], 1);
+                atomicAdd(&p.state[my_tree].plies, (unsigned long long)plies);
                 playing = false;
             }
         }

@@ -80,6 +80,7 @@ struct mctsnc_handle {
     ulonglong2 *rng_expand = nullptr;
     ulonglong2 *rng_playout_base = nullptr;
     ulonglong2 *rng_expand_base = nullptr;
+    JumpColumn *jump_cols = nullptr;      // [JUMP_LEVELS][128] matrices of the 2^64-step jump, for seeding streams on the device
     ulonglong2 *root_board = nullptr;
     signed char *root_turn = nullptr;
     WorkQueues *queue = nullptr;          // Connect 4: work queue of batched launches
@@ -439,6 +440,14 @@ void make_streams(uint64_t seed, long long first, long long count, long long str
     }
 }
 
+// the jump matrices, computed once per process
+const JumpColumn *jump_matrix_table() {
+    static JumpColumn table[JUMP_LEVELS * 128];
+    static std::once_flag once;
+    std::call_once(once, [] { jump_matrices(table); });
+    return table;
+}
+
 bool is_ocp(const mctsnc_config &c) { return c.variant == MCTSNC_OCP_THRIFTY || c.variant == MCTSNC_OCP_PRODIGAL; }
 bool is_thrifty(const mctsnc_config &c) { return c.variant == MCTSNC_OCP_THRIFTY || c.variant == MCTSNC_ACP_THRIFTY; }
 
@@ -506,6 +515,7 @@ void release(mctsnc_handle *h) {
     cudaFree(h->rng_expand);
     cudaFree(h->rng_playout_base);
     cudaFree(h->rng_expand_base);
+    cudaFree(h->jump_cols);
     cudaFree(h->root_board);
     cudaFree(h->root_turn);
     cudaFree(h->queue);
@@ -553,10 +563,12 @@ const void *search_kernel_ptr(const mctsnc_config &c) {
 
 // Threads of the block that grows one tree, from the games a step plays (n_playouts, times the children of a node for
 // the ACP variants) and from how many trees there are for the device.
-//   Many trees (at least two per SM): a quarter of the games, between 32 and 384.  Measured on 256 roots: headline ACP
-//   4 x 256 (1792 games a step) 15.2 / 15.4 / 15.1-16.8 G playouts/s at 256 / 320 / 384 threads, 14.1 at 512; OCP 8 trees
-//   x 1000 steps with 32 / 128 / 512 playouts: 4.2 / 8.2 / 17.7 G/s at 32 / 64 / 128 threads against 1.4 / 5.0 / 12.8 at
-//   384 (small blocks put more trees on an SM, which hides the latency of the select/expand/backup warp).
+//   Many trees (at least two per SM): a quarter of the games, between 32 and 320.  Measured on 256 roots: headline ACP
+//   4 x 256 (1792 games a step) 16.9 / 18.2 / 17.3 / 15.8 / 15.7 G playouts/s at 256 / 320 / 384 / 448 / 512 threads (three
+//   blocks per SM up to 384; a thread of a smaller block plays more games per step, so less of a step is spent waiting for
+//   its last games); OCP 8 trees x 1000 steps with 32 / 128 / 512 playouts: 4.2 / 8.2 / 17.7 G/s at 32 / 64 / 128 threads
+//   against 1.4 / 5.0 / 12.8 at 384 (small blocks put more trees on an SM, which hides the latency of the
+//   select/expand/backup warp).
 //   Few trees (a tree has an SM to itself): one thread per game, at most 1024; measured on one 4-tree ACP search of
 //   2000 steps: 94.7 ms with 256 threads, 69.3 ms with 512, 67.5 ms with 1024.  In between: half the games, at most 512.
 int choose_threads(mctsnc_handle *h, long long trees) {
@@ -566,7 +578,7 @@ int choose_threads(mctsnc_handle *h, long long trees) {
         return t < 32 ? 32 : (t > most ? most : t);
     };
     int threads;
-    if (trees >= 2LL * h->sm_count) threads = fit(games / 4, 384);
+    if (trees >= 2LL * h->sm_count) threads = fit(games / 4, 320);
     else if (trees <= h->sm_count) threads = fit(games, 1024);
     else threads = fit(games / 2, 512);
     const void *fn = search_kernel_ptr(h->cfg);
@@ -679,9 +691,15 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
             if (ocp) gomoku::tree_step_kernel<true><<<n, 256, 0, gs>>>(p);
             else gomoku::tree_step_kernel<false><<<n, 256, 0, gs>>>(p);
             if (s == steps) continue;
-            // one lane per game of the step at most (OCP: one child per tree, ACP: up to 225), never more than fit at once
+            // The group's share of the blocks that fit on the device at once (a quarter more, to cover groups that are
+            // between two playout launches), and never more than one lane per game of the step (OCP: one child per tree,
+            // ACP: up to 225).  A lane that plays several games one after the other keeps its warp full; a launch with a
+            // lane for every game would leave each warp waiting for the longest of its 32 games (mean ~85 plies, longest
+            // ~170).
             const long long games = (long long)n * h->cfg.n_playouts * (ocp ? 1 : h->A);
-            long long blocks = (games + gomoku::DYN_THREADS - 1) / gomoku::DYN_THREADS;
+            long long blocks = (5 * resident + 4 * groups - 1) / (4 * groups);
+            const long long enough = (games + gomoku::DYN_THREADS - 1) / gomoku::DYN_THREADS;
+            if (blocks > enough) blocks = enough;
             if (blocks > resident) blocks = resident;
             if (blocks < 1) blocks = 1;
             if (ocp) gomoku::playout_dynamic_kernel<true><<<(unsigned)blocks, gomoku::DYN_THREADS, h->dyn_smem, gs>>>(p, n);
@@ -883,7 +901,8 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     const bool ocp = is_ocp(c);
     h->rng_per_search = ocp ? (long long)c.n_trees * c.n_playouts : (long long)c.n_trees * h->A * c.n_playouts;
     h->dyn_smem = sizeof(ulonglong2) * (size_t)(h->rng_per_search / c.n_trees);
-    if (is_gomoku(c)) h->dyn_smem = sizeof(unsigned) * (size_t)gomoku::THREAD_WORDS * (gomoku::DYN_THREADS + gomoku::DYN_THREADS / 32);   // per-thread game state + per-warp templates
+    if (is_gomoku(c))   // per-thread game state + per-warp templates + the tables of the exactly-five test
+        h->dyn_smem = sizeof(unsigned) * ((size_t)gomoku::THREAD_WORDS * (gomoku::DYN_THREADS + gomoku::DYN_THREADS / 32) + gomoku::TABLE_WORDS);
     if (h->dyn_smem > 48 * 1024) {
         const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>)
                                           : search_kernel_ptr(c);
@@ -915,6 +934,8 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc) rc = dev_alloc(h, &h->rng_playout_base, h->rng_per_search);
     if (!rc) rc = dev_alloc(h, &h->rng_expand, h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->rng_expand_base, (long long)c.n_trees);
+    if (!rc) rc = dev_alloc(h, &h->jump_cols, (long long)JUMP_LEVELS * 128);
+    if (!rc) rc = (int)cudaMemcpy(h->jump_cols, jump_matrix_table(), sizeof(JumpColumn) * JUMP_LEVELS * 128, cudaMemcpyHostToDevice);
     if (!rc) rc = dev_alloc(h, &h->root_board, (long long)c.max_batch);
     if (!rc) rc = dev_alloc(h, &h->root_turn, (long long)c.max_batch);
     if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->queue, 1);
@@ -972,18 +993,19 @@ extern "C" int mctsnc_reset_rng(mctsnc_handle *h) {
     CUDA_TRY(cudaSetDevice(h->cfg.device));
     const mctsnc_config &c = h->cfg;
     const bool ocp = is_ocp(c);
-    std::vector<ulonglong2> host((size_t)h->rng_per_search);
+    RngState seeded;
+    rng_seed(seeded, c.seed);
     // playout streams: ACP stream (tree, action, t) = tree*A*P + action*P + t (src/mctsnc.py:1938, :2028),
-    // OCP stream (tree, t) = tree*P + t (cuda.grid(1), :1849); `tree` counts over the whole (sharded) search
+    // OCP stream (tree, t) = tree*P + t (cuda.grid(1), :1849); `tree` counts over the whole (sharded) search.  Every
+    // stream is computed on the device from its index (numba builds them one after the other on the host).
     const long long per_tree = ocp ? (long long)c.n_playouts : (long long)h->A * c.n_playouts;
-    make_streams(c.seed, (long long)c.tree_offset * per_tree, h->rng_per_search, 1, host.data());
-    CUDA_TRY(cudaMemcpy(h->rng_playout_base, host.data(), sizeof(ulonglong2) * host.size(), cudaMemcpyHostToDevice));
-    if (ocp) {
-        // the child pick of tree `tree` uses stream tree * tpb_e1 of a second array with the same seed (:391, :1385)
-        std::vector<ulonglong2> he((size_t)c.n_trees);
-        make_streams(c.seed, (long long)c.tree_offset * h->tpb_e1, c.n_trees, h->tpb_e1, he.data());
-        CUDA_TRY(cudaMemcpy(h->rng_expand_base, he.data(), sizeof(ulonglong2) * he.size(), cudaMemcpyHostToDevice));
-    }
+    const unsigned grid = (unsigned)((h->rng_per_search + 127) / 128 < 4096 ? (h->rng_per_search + 127) / 128 : 4096);
+    init_streams_kernel<<<grid, 128>>>(h->rng_playout_base, h->jump_cols, seeded.s0, seeded.s1, (long long)c.tree_offset * per_tree,
+                                       1, h->rng_per_search);
+    if (ocp)  // the child pick of tree `tree` uses stream tree * tpb_e1 of a second array with the same seed (:391, :1385)
+        init_streams_kernel<<<1, 128>>>(h->rng_expand_base, h->jump_cols, seeded.s0, seeded.s1,
+                                        (long long)c.tree_offset * h->tpb_e1, h->tpb_e1, c.n_trees);
+    CUDA_TRY(cudaGetLastError());
     int rc = seed_streams(h, c.max_batch, 0);
     if (rc) return rc;
     CUDA_TRY(cudaDeviceSynchronize());
@@ -1048,9 +1070,8 @@ extern "C" int mctsnc_run(mctsnc_handle *h, const int8_t *board, const int8_t *e
     return fetch_results(h, 1, h->sums, out, 0);
 }
 
-extern "C" int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards, const int8_t *extras,
-                                          const int8_t *turns, int64_t steps, int32_t reseed, int64_t *partial_sums_device,
-                                          void *stream) {
+extern "C" int mctsnc_launch_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards, const int8_t *extras,
+                                         const int8_t *turns, int64_t steps, int32_t reseed, void *stream) {
     if (!h || (boards && !turns) || batch < 1 || steps < 0 || steps > 0x7fffffff) return MCTSNC_E_BAD_ARGUMENT;
     if (batch > h->cfg.max_batch) return MCTSNC_E_CAPACITY;
     if (!boards && batch > h->staged_roots) return MCTSNC_E_BAD_ARGUMENT;  // nothing staged to search again
@@ -1072,7 +1093,23 @@ extern "C" int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const
     if (rc) return rc;
     CUDA_TRY(cudaEventRecord(h->ev1, s));
     h->last_steps = steps;
-    return launch_reduce_trees(h, batch, partial_sums_device ? (long long *)partial_sums_device : h->sums, s);
+    h->reduce_ms[0] = h->reduce_ms[1] = 0.f;
+    return 0;
+}
+
+extern "C" int mctsnc_reduce_trees_device(mctsnc_handle *h, int32_t batch, int64_t *partial_sums_device, void *stream) {
+    if (!h || batch < 1) return MCTSNC_E_BAD_ARGUMENT;
+    if (batch > h->cfg.max_batch) return MCTSNC_E_CAPACITY;
+    CUDA_TRY(cudaSetDevice(h->cfg.device));
+    return launch_reduce_trees(h, batch, partial_sums_device ? (long long *)partial_sums_device : h->sums, (cudaStream_t)stream);
+}
+
+extern "C" int mctsnc_search_batch_device(mctsnc_handle *h, int32_t batch, const int8_t *boards, const int8_t *extras,
+                                          const int8_t *turns, int64_t steps, int32_t reseed, int64_t *partial_sums_device,
+                                          void *stream) {
+    int rc = mctsnc_launch_batch_device(h, batch, boards, extras, turns, steps, reseed, stream);
+    if (rc) return rc;
+    return mctsnc_reduce_trees_device(h, batch, partial_sums_device, stream);
 }
 
 extern "C" int mctsnc_finish_batch_device(mctsnc_handle *h, int32_t batch, const int64_t *summed_device, mctsnc_result *results,

@@ -34,7 +34,7 @@ enum Reason {
 };
 constexpr int MAX_EVALUATIONS = 2;
 #ifndef PUCT_SELECT_WARPS_PER_BLOCK
-#define PUCT_SELECT_WARPS_PER_BLOCK 2
+#define PUCT_SELECT_WARPS_PER_BLOCK 1
 #endif
 constexpr int SELECT_WARPS_PER_BLOCK = PUCT_SELECT_WARPS_PER_BLOCK;  // traversals per thread block of the select kernel
 constexpr float LOWEST = -3.4028234663852886e38f;
@@ -103,7 +103,9 @@ __global__ void select_kernel(float cpuct, float c_pw, float alpha_pw, int soft_
     // puts the `warps` traversals of a tree into one block (src/puct/puct_gpu_v3_cpp.cu:472-473); with 8 traversals per
     // tree most of them lose the claim at the root and leave after two evaluations, and a block of 8 warps then keeps
     // its 6 idle warp slots until its last traversal has gone all the way down.  Small blocks give the slots back at
-    // once; the traversals of a tree still start together (their warps are neighbours in the grid).
+    // once; the traversals of a tree still start together (their warps are neighbours in the grid).  Measured on 4096
+    // trees x 64 edges x depth 16 with 8 / 1 traversals per tree: one warp per block 0.140 / 0.054 ms, two 0.140 / 0.060,
+    // four 0.149 / 0.057, eight (the reference's shape for 8) 0.307 / 0.079; the reference kernel 0.260 / 0.081.
     const int lane = threadIdx.x & 31;
     const int traversal = blockIdx.x * (int)(blockDim.x >> 5) + (int)(threadIdx.x >> 5);
     const int tree = traversal / warps;

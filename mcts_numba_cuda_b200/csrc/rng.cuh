@@ -51,7 +51,62 @@ inline void rng_jump(RngState &s) {
     s.s1 = b;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Stream i of create_xoroshiro128p_states is the seeded state jumped i times by 2^64 steps
+// (numba/cuda/random.py:226-243: a sequential chain on the host).  The state update and therefore the jump are linear
+// over GF(2), so "jump 2^k times" is a 128 x 128 bit matrix J^(2^k), and stream i is the product of the matrices of the set
+// bits of i applied to the seeded state: every stream can be computed on its own, in at most JUMP_LEVELS matrix-vector
+// products, on the device.  A matrix is stored by columns (column c = image of the state with only bit c set; bits 0..63
+// are s0, bits 64..127 are s1), so a product is the XOR of the columns selected by the set bits of the state.
+constexpr int JUMP_LEVELS = 28;   // stream indices below 2^28 (512 trees x 512 actions x 512 playouts = 2^27)
+
+struct JumpColumn {
+    unsigned long long s0, s1;
+};
+
+MCTS_HD void jump_apply(const JumpColumn *cols, unsigned long long &s0, unsigned long long &s1) {
+    unsigned long long a0 = 0, a1 = 0;
+    for (int c = 0; c < 64; c++) {
+        const unsigned long long m0 = 0ULL - ((s0 >> c) & 1ULL), m1 = 0ULL - ((s1 >> c) & 1ULL);
+        a0 ^= (cols[c].s0 & m0) ^ (cols[64 + c].s0 & m1);
+        a1 ^= (cols[c].s1 & m0) ^ (cols[64 + c].s1 & m1);
+    }
+    s0 = a0;
+    s1 = a1;
+}
+
+// fills cols[JUMP_LEVELS][128]: level 0 from rng_jump on the 128 unit states, level k+1 = level k applied to itself
+inline void jump_matrices(JumpColumn *cols) {
+    for (int c = 0; c < 128; c++) {
+        RngState s;
+        s.s0 = c < 64 ? 1ULL << c : 0ULL;
+        s.s1 = c < 64 ? 0ULL : 1ULL << (c - 64);
+        rng_jump(s);
+        cols[c].s0 = s.s0;
+        cols[c].s1 = s.s1;
+    }
+    for (int k = 1; k < JUMP_LEVELS; k++)
+        for (int c = 0; c < 128; c++) {
+            unsigned long long s0 = cols[(k - 1) * 128 + c].s0, s1 = cols[(k - 1) * 128 + c].s1;
+            jump_apply(cols + (k - 1) * 128, s0, s1);
+            cols[k * 128 + c].s0 = s0;
+            cols[k * 128 + c].s1 = s1;
+        }
+}
+
 #if defined(__CUDACC__)
+// out[i] = stream first + i * stride of create_xoroshiro128p_states(*, seed): (seed0, seed1) is the seeded state
+__global__ void init_streams_kernel(ulonglong2 *out, const JumpColumn *cols, unsigned long long seed0, unsigned long long seed1,
+                                    long long first, long long stride, long long count) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long index = (unsigned long long)(first + i * stride);
+        unsigned long long s0 = seed0, s1 = seed1;
+        for (int k = 0; k < JUMP_LEVELS; k++)
+            if ((index >> k) & 1ULL) jump_apply(cols + k * 128, s0, s1);
+        out[i] = make_ulonglong2(s0, s1);
+    }
+}
+
 // uniform float32 of numba: the 53-bit integer x >> 11 is exact in float64, so one round-to-nearest conversion of the
 // integer to float32 followed by the exact scaling 2^-53 gives the same value as float32(float64(v) * 2^-53).
 __device__ __forceinline__ float rng_uniform_f32(unsigned long long &s0, unsigned long long &s1) {

@@ -66,47 +66,90 @@ class RootParallelMCTSNC:
                             n_trees_global=world_size * n_trees, **kwargs)
         self.local.init_device_side_arrays()
         self.max_batch = max_batch
-        self._sums = None
-        self._batch = 0   # roots staged by the last call that brought boards (0: none yet; the library then refuses boards=None)
+        self._sums = None     # two buffers of partial sums, used by alternate calls
+        self._batch = 0       # roots staged by the last call that brought boards (0: none yet; the library then refuses boards=None)
+        self._calls = 0
+        self._side = None     # stream of the exchange (all-reduce + final argmax) when there is more than one rank
+        self._reduced = None  # per buffer: event "partial sums written" (main stream) ...
+        self._finished = None  # ... and event "argmax done" (exchange stream)
+
+    def _prepare(self):
+        import torch
+        if self._sums is None:
+            A = self.local.state_max_actions
+            dev = f"cuda:{self.local.device}"
+            self._sums = [torch.empty((self.max_batch, 3 * A), dtype=torch.int64, device=dev) for _ in range(2)]
+            self._reduced = [torch.cuda.Event(), torch.cuda.Event()]
+            self._finished = [None, None]
+            if self.world_size > 1:
+                self._side = torch.cuda.Stream(device=dev)
 
     def search_async(self, boards, extras, turns, steps, reseed=True, stream=None):
-        """Launches the searches, the all-reduce and the final argmax on one CUDA stream (torch's current stream, or the
-        ``cudaStream_t`` handle given as ``stream``); nothing is copied back."""
+        """Launches the searches of one batch on a CUDA stream (torch's current stream, or the ``cudaStream_t`` handle
+        given as ``stream``) and their exchange -- all-reduce of the per-action sums, final argmax -- behind them; nothing
+        is copied back.  With more than one rank the exchange runs on a stream of its own: the all-reduce is a meeting
+        point of the ranks, and on the search stream it would make every rank wait for the slowest one after every batch
+        (the ranks grow different trees, their launches differ by a few per cent).  Here the next call's searches start at
+        once; only its partial sums wait for this call's argmax, because the two share the handle's flag and statistics
+        buffers.  Results are read with ``fetch``."""
         import torch
         if stream is not None and stream != torch.cuda.current_stream().cuda_stream:
-            # the all-reduce is ordered against torch's current stream: make the given stream that one
             with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
                 return self.search_async(boards, extras, turns, steps, reseed)
         import torch.distributed as dist
-        ai = self.local
-        A = ai.state_max_actions
+        self._prepare()
+        ai, lib = self.local, _abi.lib()
         batch = max(self._batch, 1) if boards is None else len(boards)
-        if self._sums is None:
-            self._sums = torch.empty((self.max_batch, 3 * A), dtype=torch.int64, device=f"cuda:{ai.device}")
-        cu_stream = torch.cuda.current_stream().cuda_stream
+        main = torch.cuda.current_stream()
+        cu_main = ctypes.c_void_p(main.cuda_stream)
         if boards is not None:
             boards = np.ascontiguousarray(boards, dtype=np.int8)
             extras = np.ascontiguousarray(extras, dtype=np.int8) if extras is not None else None
             turns = np.ascontiguousarray(turns, dtype=np.int8)
-            self._batch = batch
-        _abi.check(_abi.lib().mctsnc_search_batch_device(
+        _abi.check(lib.mctsnc_launch_batch_device(
             ai._handle, batch, boards.ctypes.data if boards is not None else None,
             extras.ctypes.data if boards is not None and extras is not None else None,
-            turns.ctypes.data if boards is not None else None, int(steps), 1 if reseed else 0, self._sums.data_ptr(),
-            ctypes.c_void_p(cu_stream)))
-        if self.world_size > 1:
-            dist.all_reduce(self._sums[:batch], op=dist.ReduceOp.SUM, group=self.group)
-        _abi.check(_abi.lib().mctsnc_finish_batch_device(ai._handle, batch, self._sums.data_ptr(), None,
-                                                         ctypes.c_void_p(cu_stream)))
+            turns.ctypes.data if boards is not None else None, int(steps), 1 if reseed else 0, cu_main))
+        if boards is not None:
+            self._batch = batch
+        k = self._calls % 2
+        prev = self._finished[1 - k]
+        if prev is not None:
+            main.wait_event(prev)          # the previous call's argmax reads what reduce_trees is about to overwrite
+        sums = self._sums[k]
+        _abi.check(lib.mctsnc_reduce_trees_device(ai._handle, batch, sums.data_ptr(), cu_main))
+        if self._side is None:
+            _abi.check(lib.mctsnc_finish_batch_device(ai._handle, batch, sums.data_ptr(), None, cu_main))
+            self._finished[k] = None
+        else:
+            self._reduced[k].record(main)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(self._reduced[k])
+                dist.all_reduce(sums[:batch], op=dist.ReduceOp.SUM, group=self.group)
+                _abi.check(lib.mctsnc_finish_batch_device(ai._handle, batch, sums.data_ptr(), None,
+                                                          ctypes.c_void_p(self._side.cuda_stream)))
+                done = torch.cuda.Event()
+                done.record(self._side)
+            self._finished[k] = done
+        self._last = k
+        self._calls += 1
         return batch
+
+    def drain(self):
+        """Makes the current stream wait for the exchange of the last ``search_async`` call (for timing with events)."""
+        import torch
+        done = self._finished[self._last] if self._calls else None
+        if done is not None:
+            torch.cuda.current_stream().wait_event(done)
 
     def fetch(self, batch, stream=None):
         """Copies the results of the last ``search_async`` to the host (synchronises)."""
         import torch
         ai = self.local
+        self.drain()
         cu_stream = torch.cuda.current_stream().cuda_stream if stream is None else stream
         out = np.zeros(batch, dtype=_abi.RESULT_DTYPE)
-        _abi.check(_abi.lib().mctsnc_finish_batch_device(ai._handle, batch, self._sums.data_ptr(), out.ctypes.data,
+        _abi.check(_abi.lib().mctsnc_finish_batch_device(ai._handle, batch, self._sums[self._last].data_ptr(), out.ctypes.data,
                                                          ctypes.c_void_p(cu_stream)))
         return out
 

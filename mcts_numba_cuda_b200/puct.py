@@ -24,6 +24,10 @@ def _lib():
         L.puct_select_virtual_loss_launch.restype = i32
         L.puct_backup_launch.argtypes = [i32] + [vp] * 9 + [i32] * 5 + [vp]
         L.puct_backup_launch.restype = i32
+        L.puct_v2_select_launch.argtypes = [i32, f32, f32, f32] + [vp] * 11 + [i32] * 5 + [vp]
+        L.puct_v2_select_launch.restype = i32
+        L.puct_v2_backup_launch.argtypes = [i32] + [vp] * 10 + [i32] * 5 + [vp]
+        L.puct_v2_backup_launch.restype = i32
         L.puct_cpp_cuda_error_string.argtypes = [i32]
         L.puct_cpp_cuda_error_string.restype = ctypes.c_char_p
         _configured = True
@@ -88,6 +92,30 @@ def launch_backup(d, values=None, virtual_loss=1, stream=None):
 
 def launch_release(d, virtual_loss=1, stream=None):
     launch_backup(d, None, virtual_loss, stream)
+
+
+V2_PRECLAIM, V2_COUNTER_CAS = 0, 1
+
+
+def launch_select_v2(d, cpuct=1.0, c_pw=1.0, alpha_pw=0.5, variant=V2_PRECLAIM, stream=None):
+    """The two older select kernels of the reference (``src/puct/puct_gpu_v2.py:573-840``), for trees that keep virtual
+    visits per child node: ``d`` holds ``node_inflight`` (int32[trees, nodes]) in place of ``edge_inflight``.
+    ``variant``: preclaim (every candidate is visited before it is scored, losers leave) or counter-CAS (the winner alone
+    is claimed by compare-and-swap; a claim that met other visits is given back once)."""
+    trees, nodes, edges, warps, path_depth = _shape(d)
+    args = [_ptr(d[k]) for k in ("edge_child", "edge_prior", "edge_w", "edge_n", "node_inflight", "node_expand_inflight",
+                                 "node_expanded", "node_count", "out_selected", "out_path", "out_len")]
+    _check(_lib().puct_v2_select_launch(int(variant), cpuct, c_pw, alpha_pw, *args, trees, nodes, edges, warps, path_depth,
+                                        _stream(stream)), "v2 select")
+
+
+def launch_backup_v2(d, values=None, virtual_loss=1, stream=None):
+    """``_backup_kernel_native`` of ``src/puct/puct_gpu_v2.py:847-927`` (``values=None``: release only)."""
+    trees, nodes, edges, warps, path_depth = _shape(d)
+    _check(_lib().puct_v2_backup_launch(int(virtual_loss), _ptr(d["edge_child"]), _ptr(d["edge_w"]), _ptr(d["edge_n"]),
+                                        _ptr(d["node_inflight"]), _ptr(d["node_expand_inflight"]), _ptr(d["node_count"]),
+                                        _ptr(d["out_selected"]), _ptr(d["out_path"]), _ptr(d["out_len"]), _ptr(values), trees,
+                                        nodes, edges, warps, path_depth, _stream(stream)), "v2 backup")
 
 
 def to_device(case, device="cuda"):

@@ -36,6 +36,26 @@ def test_streams_equal_numba_layout():
     assert np.array_equal(_streams(ocp, 1, 3), ref[[0, 64, 128]])   # tpb_e1 = 64 for Connect 4
 
 
+def test_streams_seeded_on_the_device_equal_the_sequential_chain_for_a_large_configuration():
+    """The streams are computed on the device, each from its own index (products of jump matrices); numba and the oracle
+    build them one after the other.  Gomoku 4 x 225 x 256 = 230 400 streams, and a shard that starts far into the chain."""
+    n = 4 * 225 * 256
+    ai = MCTSNC((15, 15), 0, 225, search_steps_limit=2, search_time_limit=np.inf, n_trees=4, n_playouts=256, variant="acp_prodigal",
+                device_memory=16.0, seed=11, verbose_info=False)
+    ai.init_device_side_arrays()
+    ref = om.rng_states(n, 11)
+    assert np.array_equal(_streams(ai, 0, n), ref)
+    shard = MCTSNC((15, 15), 0, 225, search_steps_limit=2, search_time_limit=np.inf, n_trees=1, n_playouts=256,
+                   variant="acp_prodigal", device_memory=16.0, seed=11, verbose_info=False, tree_offset=3, n_trees_global=4)
+    shard.init_device_side_arrays()
+    assert np.array_equal(_streams(shard, 0, 225 * 256), ref[3 * 225 * 256:])
+    ocp = MCTSNC((15, 15), 0, 225, search_steps_limit=2, search_time_limit=np.inf, n_trees=3, n_playouts=64, variant="ocp_thrifty",
+                 device_memory=16.0, seed=11, verbose_info=False, tree_offset=2, n_trees_global=5)
+    ocp.init_device_side_arrays()
+    assert np.array_equal(_streams(ocp, 0, 3 * 64), ref[2 * 64:5 * 64])
+    assert np.array_equal(_streams(ocp, 1, 3), ref[[2 * 256, 3 * 256, 4 * 256]])   # tpb_e1 = 256 for Gomoku
+
+
 def test_sharded_streams_are_a_slice_of_the_global_ones():
     kw = dict(search_steps_limit=5, search_time_limit=np.inf, n_playouts=32, variant="acp_thrifty", seed=7, verbose_info=False)
     part = MCTSNC((6, 7), 7, 7, n_trees=2, tree_offset=4, n_trees_global=8, **kw)
@@ -288,7 +308,7 @@ def test_queued_batch_matches_oracle(variant):
 
 
 @pytest.mark.parametrize("variant,n_trees,n_playouts,roots,threads", [
-    ("acp_prodigal", 4, 256, 128, 384),     # many trees, 1792 games a step: a quarter of the games, capped
+    ("acp_prodigal", 4, 256, 128, 320),     # many trees, 1792 games a step: a quarter of the games, capped
     ("ocp_prodigal", 8, 32, 64, 32),        # many trees, 32 games a step: one warp
     ("ocp_prodigal", 8, 512, 64, 128),
     ("acp_prodigal", 4, 256, 1, 1024),      # a tree has an SM to itself: one thread per game, capped
