@@ -92,6 +92,8 @@ def parse_args():
     ap.add_argument("--internal", default="", help=argparse.SUPPRESS)
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations and the reference's own runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="multi-GPU exchange of the per-action sums: NCCL all-reduce, or the library's own peer stores and flags")
     return ap.parse_args()
 
 
@@ -641,7 +643,7 @@ def main():
     searcher = RootParallelMCTSNC(G["shape"], G["extra"], A, n_trees=args.trees, n_playouts=args.playouts, variant=args.variant,
                                   search_steps_limit=args.search_steps, max_batch=B, device=local_rank, rank=rank,
                                   world_size=world, seed=0, ucb_c=2.0, threads_per_tree=args.threads_per_tree,
-                                  device_memory=16.0 if args.game == "gomoku" else 2.0)
+                                  device_memory=16.0 if args.game == "gomoku" else 2.0, exchange=args.exchange)
 
     def barrier():
         if world > 1:
@@ -680,6 +682,7 @@ def main():
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
     parity = multi_gpu_parity(args, searcher, boards, fills, turns, rank, world, local_rank) if world > 1 else None
+    exchange_status = searcher.exchange_status()
     # max over ranks of the timed regions, sums of the work
     stats = torch.tensor([dev_ms, e2e_s * 1e3, kernel_ms], dtype=torch.float64, device="cuda")
     work = torch.tensor([local_playouts, local_plies], dtype=torch.int64, device="cuda")
@@ -737,7 +740,8 @@ def main():
         "clocks": clocks, "threads_per_tree": geo["threads_per_tree"], "blocks_per_sm": per_sm,
         "device_bytes": geo["device_bytes"], "status_bits": status, "ub_draws_per_pass": ub_draws,
         "playouts_per_pass": playouts_per_pass, "best_action_checksum": int(out["best_action"].astype(np.int64).sum()),
-        "multi_gpu_parity": parity,
+        "multi_gpu_parity": parity, "exchange": args.exchange if n_gpus > 1 else None,
+        "exchange_status": exchange_status,
     }
     if n_gpus == 1 and not args.no_cpu_baseline:
         steps = args.cpu_sample_steps or 400

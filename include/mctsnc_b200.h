@@ -209,6 +209,27 @@ int mctsnc_read_slices(mctsnc_handle *h, int64_t *dst, int32_t max_records, int3
 int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_info, int32_t turn, int32_t variant, int32_t n_trees,
                             int32_t n_playouts, int64_t steps, float ucb_c, uint64_t seed, int64_t *out_device, void *stream);
 
+/* Exchange step of root-parallel search over the GPUs of one box without a collective library (no counterpart in the
+   reference, which is single-GPU): in-place sum over `world` ranks of an int64 vector that lives on each rank's device --
+   the partial sums of mctsnc_reduce_trees_device.  Every rank stores its vector into every peer's buffer (plain peer
+   stores over NVLink), raises a flag there and adds up what arrived in its own buffer; remote memory is only written.
+   One process per GPU: create() allocates the local buffer on `device` and returns its CUDA IPC handle
+   (MCTSNC_EXCHANGE_HANDLE_BYTES bytes); the ranks exchange the handles by any means (the Python wrapper uses
+   torch.distributed.all_gather_object) and pass all of them, in rank order, to connect().  connect(ex, NULL) maps every
+   peer onto the local buffer (loop-back, for tests).  allreduce() queues two small kernels on `stream`; the wait for the
+   peers' flags gives up after wait_limit polls of about a quarter of a microsecond each, sets MCTSNC_EXCHANGE_TIMEOUT in
+   the status word (sticky; read with status(), which synchronises the stream) and leaves the values as they were.
+   Every rank must make the same sequence of allreduce calls. */
+#define MCTSNC_EXCHANGE_HANDLE_BYTES 64
+#define MCTSNC_EXCHANGE_TIMEOUT 1
+typedef struct mctsnc_exchange mctsnc_exchange;
+int mctsnc_exchange_create(int32_t rank, int32_t world, int64_t n_values_max, int32_t device, mctsnc_exchange **out,
+                           unsigned char *ipc_handle_out);
+int mctsnc_exchange_connect(mctsnc_exchange *ex, const unsigned char *all_handles);
+int mctsnc_exchange_allreduce(mctsnc_exchange *ex, int64_t *values_device, int64_t n, int32_t wait_limit, void *stream);
+int mctsnc_exchange_status(mctsnc_exchange *ex, int32_t *status_out, void *stream);
+int mctsnc_exchange_destroy(mctsnc_exchange *ex);
+
 /* Text for a return code of any function above (cf. puct_cpp_cuda_error_string, src/puct/puct_gpu_v3_cpp.cu:483-485). */
 const char *mctsnc_error_string(int code);
 

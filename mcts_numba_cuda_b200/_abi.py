@@ -23,7 +23,10 @@ E_BAD_ARGUMENT, E_UNSUPPORTED, E_NO_MEMORY, E_BAD_ROOT, E_CAPACITY, E_NO_DEVICE 
 EXPORTED = ["mctsnc_create", "mctsnc_destroy", "mctsnc_reset_rng", "mctsnc_run", "mctsnc_run_batch",
             "mctsnc_search_batch_device", "mctsnc_finish_batch_device", "mctsnc_launch_batch_device",
             "mctsnc_reduce_trees_device", "mctsnc_export", "mctsnc_export_rng",
-            "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_trace_slices", "mctsnc_read_slices", "mctsnc_error_string"]
+            "mctsnc_query", "mctsnc_search_c4_static", "mctsnc_trace_slices", "mctsnc_read_slices",
+            "mctsnc_exchange_create", "mctsnc_exchange_connect", "mctsnc_exchange_allreduce", "mctsnc_exchange_status",
+            "mctsnc_exchange_destroy", "mctsnc_error_string"]
+EXCHANGE_HANDLE_BYTES, EXCHANGE_TIMEOUT = 64, 1
 # the PUCT entry points keep the names of the reference's native library (include/puct_b200.h)
 EXPORTED_PUCT = ["puct_select_winner_recalc_launch", "puct_select_virtual_loss_launch", "puct_backup_launch",
                  "puct_cpp_cuda_error_string", "puct_v2_select_launch", "puct_v2_backup_launch"]
@@ -94,6 +97,11 @@ def lib():
         L.mctsnc_export_rng.argtypes = [vp, i32, i32, vp, i64]
         L.mctsnc_query.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i64)]
         L.mctsnc_search_c4_static.argtypes = [vp, vp, i32, i32, i32, i32, i64, ctypes.c_float, ctypes.c_uint64, vp, vp]
+        L.mctsnc_exchange_create.argtypes = [i32, i32, i64, i32, ctypes.POINTER(vp), vp]
+        L.mctsnc_exchange_connect.argtypes = [vp, vp]
+        L.mctsnc_exchange_allreduce.argtypes = [vp, vp, i64, i32, vp]
+        L.mctsnc_exchange_status.argtypes = [vp, ctypes.POINTER(i32), vp]
+        L.mctsnc_exchange_destroy.argtypes = [vp]
         L.mctsnc_trace_slices.argtypes = [vp, i32]
         L.mctsnc_read_slices.argtypes = [vp, vp, i32, ctypes.POINTER(i32)]
         L.mctsnc_error_string.argtypes = [ctypes.c_int]

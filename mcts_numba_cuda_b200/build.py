@@ -6,7 +6,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libmctsnc_b200.so")
-SOURCES = [os.path.join(HERE, "csrc", n) for n in ("mctsnc_abi.cu", "puct_select.cu", "puct_select_v2.cu", "duct_select.cu")]
+SOURCES = [os.path.join(HERE, "csrc", n) for n in ("mctsnc_abi.cu", "peer_exchange.cu", "puct_select.cu", "puct_select_v2.cu", "duct_select.cu")]
 HEADERS = [os.path.join(HERE, "csrc", n) for n in ("c4_search.cuh", "gomoku_search.cuh", "common.cuh", "rng.cuh")] + [
     os.path.join(ROOT, "include", "mctsnc_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",

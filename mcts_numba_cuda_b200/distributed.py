@@ -50,6 +50,57 @@ def reduce_over_actions_host(actions_win_flags, actions_ns, actions_ns_wins, exp
     return best, bool(keys[0][0]), keys[0][1], keys[0][2]
 
 
+class PeerExchange:
+    """In-place sum of an int64 CUDA tensor over the ranks of one box by peer stores and flags
+    (``mctsnc_exchange_*`` of ``include/mctsnc_b200.h``, ``csrc/peer_exchange.cu``), one process per GPU.  The CUDA IPC
+    handles of the ranks' buffers travel through ``torch.distributed.all_gather_object``; nothing else uses the process
+    group.  ``loopback=True`` maps every peer onto the local buffer (tests on one GPU)."""
+
+    DEFAULT_WAIT_LIMIT = 1 << 23      # polls of ~0.25 us: about two seconds before a missing rank is reported
+
+    def __init__(self, rank, world_size, n_values_max, device, group=None, loopback=False):
+        lib = _abi.lib()
+        self.rank, self.world_size = rank, world_size
+        self._ex = ctypes.c_void_p()
+        mine = (ctypes.c_ubyte * _abi.EXCHANGE_HANDLE_BYTES)()
+        _abi.check(lib.mctsnc_exchange_create(rank, world_size, int(n_values_max), int(device), ctypes.byref(self._ex), mine))
+        if loopback or world_size == 1:
+            _abi.check(lib.mctsnc_exchange_connect(self._ex, None))
+        else:
+            import torch.distributed as dist
+            gathered = [None] * world_size
+            dist.all_gather_object(gathered, bytes(mine), group=group)
+            blob = (ctypes.c_ubyte * (_abi.EXCHANGE_HANDLE_BYTES * world_size)).from_buffer_copy(b"".join(gathered))
+            _abi.check(lib.mctsnc_exchange_connect(self._ex, blob))
+            dist.barrier(group=group)          # every rank has opened every buffer before anybody stores into one
+
+    def all_reduce(self, values, wait_limit=None, stream=None):
+        """Queues the sum on a CUDA stream (torch's current stream unless a ``cudaStream_t`` handle is given)."""
+        import torch
+        cu = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        _abi.check(_abi.lib().mctsnc_exchange_allreduce(self._ex, values.data_ptr(), values.numel(),
+                                                        int(wait_limit or self.DEFAULT_WAIT_LIMIT), ctypes.c_void_p(cu)))
+
+    def status(self, stream=None):
+        """Status word (``_abi.EXCHANGE_TIMEOUT`` once a wait has run out); synchronises the stream."""
+        import torch
+        cu = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        out = ctypes.c_int32(0)
+        _abi.check(_abi.lib().mctsnc_exchange_status(self._ex, ctypes.byref(out), ctypes.c_void_p(cu)))
+        return out.value
+
+    def close(self):
+        if getattr(self, "_ex", None):
+            _abi.lib().mctsnc_exchange_destroy(self._ex)
+            self._ex = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class RootParallelMCTSNC:
     """``MCTSNC`` sharded over the ranks of an initialised ``torch.distributed`` process group (backend nccl).
 
@@ -58,8 +109,11 @@ class RootParallelMCTSNC:
     """
 
     def __init__(self, state_board_shape, state_extra_info_memory, state_max_actions, n_trees, n_playouts, variant,
-                 search_steps_limit, max_batch, device, rank, world_size, process_group=None, **kwargs):
-        self.rank, self.world_size, self.group = rank, world_size, process_group
+                 search_steps_limit, max_batch, device, rank, world_size, process_group=None, exchange="nccl", **kwargs):
+        if exchange not in ("nccl", "peer"):
+            raise ValueError(f"exchange must be 'nccl' or 'peer', not {exchange!r}")
+        self.rank, self.world_size, self.group, self.exchange = rank, world_size, process_group, exchange
+        self._peer = None
         self.local = MCTSNC(state_board_shape, state_extra_info_memory, state_max_actions, search_time_limit=np.inf,
                             search_steps_limit=search_steps_limit, n_trees=n_trees, n_playouts=n_playouts, variant=variant,
                             verbose_info=False, device=device, max_batch=max_batch, tree_offset=rank * n_trees,
@@ -83,6 +137,8 @@ class RootParallelMCTSNC:
             self._finished = [None, None]
             if self.world_size > 1:
                 self._side = torch.cuda.Stream(device=dev)
+                if self.exchange == "peer":   # peer stores and flags instead of the NCCL all-reduce
+                    self._peer = PeerExchange(self.rank, self.world_size, self.max_batch * 3 * A, self.local.device, self.group)
 
     def search_async(self, boards, extras, turns, steps, reseed=True, stream=None):
         """Launches the searches of one batch on a CUDA stream (torch's current stream, or the ``cudaStream_t`` handle
@@ -125,7 +181,10 @@ class RootParallelMCTSNC:
             self._reduced[k].record(main)
             with torch.cuda.stream(self._side):
                 self._side.wait_event(self._reduced[k])
-                dist.all_reduce(sums[:batch], op=dist.ReduceOp.SUM, group=self.group)
+                if self._peer is not None:
+                    self._peer.all_reduce(sums[:batch])
+                else:
+                    dist.all_reduce(sums[:batch], op=dist.ReduceOp.SUM, group=self.group)
                 _abi.check(lib.mctsnc_finish_batch_device(ai._handle, batch, sums.data_ptr(), None,
                                                           ctypes.c_void_p(self._side.cuda_stream)))
                 done = torch.cuda.Event()
@@ -134,6 +193,13 @@ class RootParallelMCTSNC:
         self._last = k
         self._calls += 1
         return batch
+
+    def exchange_status(self):
+        """0, or ``_abi.EXCHANGE_TIMEOUT`` once a wait of the peer exchange has run out (a rank did not arrive in time:
+        results since then are sums over the local trees only).  Always 0 with the NCCL exchange."""
+        if self._peer is None:
+            return 0
+        return self._peer.status(self._side.cuda_stream)
 
     def drain(self):
         """Makes the current stream wait for the exchange of the last ``search_async`` call (for timing with events)."""
