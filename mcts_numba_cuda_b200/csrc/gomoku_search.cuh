@@ -562,6 +562,9 @@ constexpr int LIST_WORDS = 57, ROW_WORDS = 15, THREAD_WORDS = LIST_WORDS + ROW_W
 // the mover's stone k - 5 cells along the line): set iff the stones next to the middle add up to exactly 4;
 // then per board row two masks of the window cells that exist for the lines that cross rows.
 constexpr int FIVE_WORDS = 2048 / 32, TABLE_WORDS = FIVE_WORDS + 2 * M;
+#ifndef MCTSNC_GOMOKU_FIVE_TABLE
+#define MCTSNC_GOMOKU_FIVE_TABLE 1
+#endif
 
 __device__ __forceinline__ int turn_at_start(int mode, int sel_turn) { return mode == MODE_TREE_FULL ? sel_turn : -sel_turn; }
 
@@ -752,15 +755,14 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 atomicAdd(&st->ub_draws, (unsigned long long)er.ub);
                 atomicOr(&st->status, STATUS_UB_DRAW | (er.err ? STATUS_INTERNAL : 0u));
             } else {
-                // last_action = legal[ord]; legal[ord] = legal[count - 1]; count -= 1   (:2062, :215-217)
-                const int wl = (count - 1) >> 2, wo = ord >> 2;
-                const unsigned word_last = my[wl * DYN_THREADS];
-                const unsigned last = (word_last >> (8 * ((count - 1) & 3))) & 0xFFu;
-                unsigned word_ord = wo == wl ? word_last : my[wo * DYN_THREADS];
-                const int sh = 8 * (ord & 3);
-                const int a = (word_ord >> sh) & 0xFFu;
-                word_ord = (word_ord & ~(0xFFu << sh)) | (last << sh);
-                my[wo * DYN_THREADS] = word_ord;
+                // last_action = legal[ord]; legal[ord] = legal[count - 1]; count -= 1   (:2062, :215-217).  List entry q of this
+                // thread is byte q & 3 of its word q >> 2: byte loads and stores, no read-modify-write of words
+                unsigned char *list = reinterpret_cast<unsigned char *>(my);
+                const int q_last = count - 1;
+                const unsigned char last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
+                unsigned char *at_ord = list + ((ord >> 2) * DYN_THREADS) * 4 + (ord & 3);
+                const int a = *at_ord;
+                *at_ord = last;
                 count--;
                 const int i = (a * 137) >> 11;   // a / 15 for a < 225
                 const int j = a - i * N;
@@ -786,6 +788,7 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                     const unsigned half = 0x7FFFu << hs;
                     const int rot = (17 + j + hs) & 31;
                     const unsigned gh = __funnelshift_r(row & half, row & half, rot);
+#if MCTSNC_GOMOKU_FIVE_TABLE
                     unsigned gv = 0, x = 0, y = 0;
 #pragma unroll
                     for (int r = 1; r <= 5; r++) {
@@ -808,6 +811,33 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                     const unsigned wh = (gh >> 10) & 0x7FFu, wv = (gv >> 10) & 0x7FFu, wd = (gd >> 10) & 0x7FFu, wa = (ga >> 10) & 0x7FFu;
                     win = (((s_five[wh >> 5] >> (wh & 31)) | (s_five[wv >> 5] >> (wv & 31)) | (s_five[wd >> 5] >> (wd & 31)) |
                             (s_five[wa >> 5] >> (wa & 31))) & 1u) != 0;
+#else
+                    // the runs of stones next to bit 15 are counted with find-first-set / count-leading-zeros; rows outside
+                    // the board are not masked when read, a run is cut to the rows that exist on its side instead
+                    unsigned gv = 0, x = 0, y = 0;
+#pragma unroll
+                    for (int r = 1; r <= 5; r++) {
+                        const unsigned both = (1u << (15 - r)) | (1u << (15 + r));
+                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;                      // row i - r
+                        const unsigned up = __funnelshift_r(up_w, up_w, rot);
+                        gv |= (up >> r) & (1u << (15 - r));
+                        x |= up & both;                                                            // (i - r, j - r), (i - r, j + r)
+                        const int rd = min(i + r, M - 1);                                          // row i + r
+                        const unsigned dn_w = my[(LIST_WORDS + rd) * DYN_THREADS] & half;
+                        const unsigned dn = __funnelshift_r(dn_w, dn_w, rot);
+                        gv |= (dn << r) & (1u << (15 + r));
+                        y |= dn & both;                                                            // (i + r, j + r), (i + r, j - r)
+                    }
+                    const unsigned below15 = 0x7C00u, above15 = 0x1F0000u;                         // bits 10..14, 16..20
+                    const unsigned gd = (x & below15) | (y & above15);                             // (i - r, j - r) .. (i + r, j + r)
+                    const unsigned ga = (x & above15) | (y & below15);                             // (i - r, j + r) .. (i + r, j - r)
+                    const int rows_up = i, rows_dn = M - 1 - i;
+                    const int h_hi = __ffs(~(gh >> 16)) - 1, h_lo = __clz(~(gh << 17));
+                    const int v_hi = min(__ffs(~(gv >> 16)) - 1, rows_dn), v_lo = min(__clz(~(gv << 17)), rows_up);
+                    const int d_hi = min(__ffs(~(gd >> 16)) - 1, rows_dn), d_lo = min(__clz(~(gd << 17)), rows_up);
+                    const int a_hi = min(__ffs(~(ga >> 16)) - 1, rows_up), a_lo = min(__clz(~(ga << 17)), rows_dn);
+                    win = (h_hi + h_lo == 4) | (v_hi + v_lo == 4) | (d_hi + d_lo == 4) | (a_hi + a_lo == 4);
+#endif
                 }
                 if (win) outcome = turn;
                 else if (count == 0) outcome = 0;
