@@ -681,6 +681,7 @@ def main():
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
+    geo = searcher.local.launch_geometry()   # of the timed launches (the parity check below launches a smaller search)
     parity = multi_gpu_parity(args, searcher, boards, fills, turns, rank, world, local_rank) if world > 1 else None
     exchange_status = searcher.exchange_status()
     # max over ranks of the timed regions, sums of the work
@@ -698,7 +699,6 @@ def main():
     pk = peaks()
     value = playouts_per_pass * args.steps / (dev_ms * 1e-3)
     e2e_value = playouts_per_pass * args.steps / (e2e_ms * 1e-3)
-    geo = searcher.local.launch_geometry()
     sm_count, per_sm = geo["sm_count"], geo["blocks_per_sm"]
     # dominant kernel: the search kernel.  Per rank and launch it plays plies_per_pass / n_gpus plies.
     plies_per_launch = plies_per_pass / n_gpus

@@ -1,7 +1,7 @@
 // Sum of small int64 vectors over the GPUs of one box without a collective library: every rank stores its vector
 // into a slot of every peer's buffer (plain stores to peer memory over NVLink), raises a flag there, waits -- bounded --
 // for the flags of all ranks in its own buffer and adds the slots up locally.  Remote data is only ever written, reads
-// are local.  No multicast of any kind.
+// are local.  Plain stores and loads only.
 //
 // The exchange step of root-parallel search: per batch and rank 3 * max_actions int64 per search, a few tens of KB (the
 // reference is single-GPU: its _reduce_over_trees_* sums over trees of one device, src/mctsnc.py:2223-2296; sharding the

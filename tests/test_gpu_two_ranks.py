@@ -25,6 +25,7 @@ def _worker(rank, world, port, out_dir):
     from mcts_numba_cuda_b200.roots import c4_random_roots
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
     ok = {}
