@@ -47,6 +47,7 @@ struct StepInfo {
     int pending;      // 1: playouts of this step have been launched, their backup is still to be done
     int n_active;     // children that need real playouts this step (their ranks: Params::active_rank)
     int game_counter; // next game of the step to hand out (game = active child index * P + t)
+    int n_empty;      // empty cells of the selected node's position
 };
 
 struct Params {
@@ -63,6 +64,7 @@ struct Params {
     signed char *child_outcome;  // [trees][A]   by rank: outcome of the child (2 = ongoing)
     unsigned char *child_action; // [trees][A]   by rank: action of the child
     unsigned char *active_rank;  // [trees][A]   ranks of the children that need real playouts, ascending
+    unsigned *tpl;               // [trees][TPL_WORDS]  the selected node's position in the form the playouts use
     ulonglong2 *rng_playout;
     ulonglong2 *rng_expand;
     const unsigned *root_board;  // [batch][16]
@@ -133,6 +135,33 @@ __device__ __forceinline__ unsigned block_argmax(unsigned key, unsigned tie, uns
     __syncthreads();
     return tbest;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// A game in progress, as the playouts keep it (per thread in shared memory; the same words per tree in Params::tpl for
+// the selected node, written by the tree step and copied by the playouts):
+//   LIST_WORDS words   the list of legal actions, one byte each, in the order the reference's swap-remove leaves them
+//                      (src/mctsnc_game_mechanics.py:209-217); the byte of cell (i, j) is i * 16 + j, row and column ready
+//                      to use;
+//   LINE_WORDS words   the stones by line, one word per line of each of the four directions, stones of -1 in bits 0..14,
+//                      stones of +1 in bits 16..30, at the bit of their position along the line:
+//                        row i                     (position j)
+//                        column j                  (position i)
+//                        diagonal (i - j + 14) & 15   (position j)
+//                        anti-diagonal (i + j) & 15   (position j)
+//                      A stone is set in four words, and the exactly-five test of a direction reads one word.  Cells that do
+//                      not exist are never set, so no line needs a mask.  The 29 diagonals fold into 16 words: i - j + 14 =
+//                      d <= 12 and d + 16 share a word, d occupies the positions 14 - d .. 14 and d + 16 the positions
+//                      0 .. 12 - d, with position 13 - d between them always empty: a run of stones cannot pass from one to
+//                      the other and finds the empty position where the board ends.  Likewise i + j = a <= 12 (positions
+//                      0 .. a) and a + 16 (positions a + 2 .. 14).
+constexpr int LIST_WORDS = 57, LINE_WORDS = 15 + 15 + 16 + 16, THREAD_WORDS = LIST_WORDS + LINE_WORDS;
+constexpr int LINE_ROW = LIST_WORDS, LINE_COL = LINE_ROW + 15, LINE_DIAG = LINE_COL + 15, LINE_ANTI = LINE_DIAG + 16;
+// Params::tpl keeps the two parts on 16-byte boundaries, so that a playout thread copies them four words at a time
+constexpr int TPL_LIST = 0, TPL_LINES = 60, TPL_WORDS = 124;
+// Table of the exactly-five test: one byte per 11-cell window of a line (the new stone at bit 5, five cells either way; bit
+// k = the mover's stone k - 5 positions along): 1 iff the stones next to the middle add up to exactly 4, which is what the
+// reference asks for (it counts at most 5 stones either way and wants a total of 4, src/mctsnc_game_mechanics.py:220-272).
+constexpr int FIVE_BYTES = 2048;
 
 // ---------------------------------------------------------------------------------------------------------------
 // one block of 256 threads per tree
@@ -353,6 +382,45 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
         }
         __syncthreads();
         const int n_legal = s_prefix[8];
+        {
+            // the position in the playouts' form: the list of empty cells in ascending order, the stones by line
+            unsigned *tpl = p.tpl + (long long)g * TPL_WORDS;
+            unsigned char *tpl_list = reinterpret_cast<unsigned char *>(tpl + TPL_LIST);
+            if (tid < A) {
+                const int w = tid >> 5, bit = tid & 31;
+                const unsigned empty = ~(s_board[w] | s_board[8 + w]);
+                if ((empty >> bit) & 1u)
+                    tpl_list[s_prefix[w] + __popc(empty & ((1u << bit) - 1u))] = (unsigned char)(((tid / N) << 4) | (tid % N));
+            }
+            if (tid < LINE_WORDS) {
+                const int family = tid < 15 ? 0 : (tid < 30 ? 1 : (tid < 46 ? 2 : 3));
+                const int idx = tid - (family == 0 ? 0 : (family == 1 ? 15 : (family == 2 ? 30 : 46)));
+                unsigned word = 0;
+                for (int pos = 0; pos < 15; pos++) {
+                    for (int fold = 0; fold < 2; fold++) {   // the two lines of a folded word; rows and columns have one
+                        int i, j;
+                        if (family == 0) {
+                            i = idx;
+                            j = pos;
+                        } else if (family == 1) {
+                            i = pos;
+                            j = idx;
+                        } else if (family == 2) {
+                            j = pos;
+                            i = idx + 16 * fold - 14 + j;
+                        } else {
+                            j = pos;
+                            i = idx + 16 * fold - j;
+                        }
+                        if ((family < 2 && fold == 1) || i < 0 || i >= M) continue;
+                        const int c = i * N + j;
+                        if ((s_board[c >> 5] >> (c & 31)) & 1u) word |= 1u << pos;
+                        if ((s_board[8 + (c >> 5)] >> (c & 31)) & 1u) word |= 1u << (16 + pos);
+                    }
+                }
+                tpl[TPL_LINES + tid] = word;
+            }
+        }
         const int size = st->size;
         long long room = p.node_limit - (long long)size;
         if (room < 0) room = 0;
@@ -446,6 +514,7 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
             n_active = 1;
         }
         si->n_active = n_active;
+        si->n_empty = mode == MODE_TERMINAL ? 0 : s_prefix[8];
         si->game_counter = 0;
         si->pending = 1;
         st->selected = node;
@@ -551,65 +620,60 @@ __device__ __noinline__ EmuResult playout_emulated(const unsigned *start /* 16 w
     return r;
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// Per-thread game state lives in shared memory, laid out so that every thread owns one bank column: word k of thread t
-// is s_mem[k * DYN_THREADS + t].  57 words hold the list of legal actions (one byte each, in the order the reference's
-// swap-remove leaves them, src/mctsnc_game_mechanics.py:209-217), 15 words hold the board rows (low half: stones of
-// -1, high half: stones of +1).
-constexpr int LIST_WORDS = 57, ROW_WORDS = 15, THREAD_WORDS = LIST_WORDS + ROW_WORDS;
-// Tables of the exactly-five test, behind the per-thread and per-warp words of the block's shared memory:
-// FIVE_WORDS words = one bit per 11-cell window (the new stone in the middle, five cells either way; bit k of the index =
-// the mover's stone k - 5 cells along the line): set iff the stones next to the middle add up to exactly 4;
-// then per board row two masks of the window cells that exist for the lines that cross rows.
-constexpr int FIVE_WORDS = 2048 / 32, TABLE_WORDS = FIVE_WORDS + 2 * M;
-#ifndef MCTSNC_GOMOKU_FIVE_TABLE
-#define MCTSNC_GOMOKU_FIVE_TABLE 1
-#endif
-
 __device__ __forceinline__ int turn_at_start(int mode, int sel_turn) { return mode == MODE_TREE_FULL ? sel_turn : -sel_turn; }
 
 // ---------------------------------------------------------------------------------------------------------------
-// The same playouts with games handed out to lanes one by one: a persistent grid of 256-thread blocks; every warp
+// The playouts, with games handed out to lanes one by one: a persistent grid of DYN_THREADS-thread blocks; every warp
 // works through the games of one tree's step (game = active child * P + t, taken with one atomicAdd per refill by
 // the warp's idle lanes together), then moves on to the next tree that still has games.  A lane that finishes its game
-// waits until at least REFILL_MIN lanes of its warp are idle (a refill costs ~250 instructions, mostly the copy of the
-// legal-action list; doing it for several lanes at once keeps it a small fraction of the playing).  Which lane plays a
-// game does not matter: game (child, t) draws from the stream of the reference's thread (tree, action, t).
-// Per warp a template of the parent position (list of empty cells, rows) sits in shared memory; a child's list is the
-// parent's without the child's own cell (the reference builds it by scanning the child's board in ascending order).
-constexpr int REFILL_MIN = 4;
-constexpr int DYN_THREADS = 256;
+// waits until at least REFILL_MIN lanes of its warp are idle (a refill costs a few hundred instructions, mostly the copy
+// of the legal-action list; doing it for several lanes at once keeps it a small fraction of the playing).  Which lane
+// plays a game does not matter: game (child, t) draws from the stream of the reference's thread (tree, action, t).
+// Per warp a copy of the parent position (Params::tpl) sits in shared memory; a child's list is the parent's without the
+// child's own cell (the reference builds it by scanning the child's board in ascending order).
+//
+// Per-thread game state lives in shared memory, laid out so that every thread owns one bank column: word k of thread t
+// is s_mem[k * DYN_THREADS + t].  That state (476 bytes) decides how many games an SM plays at once: two blocks of 224
+// threads.  With so few warps the kernel is bound by the latency of a warp's own instruction chain, not by issue
+// slots, which is what the choices below answer (Gomoku 15x15 acp_prodigal 4 x 256, 500 steps, one / eight searches,
+// M playouts/s): a look at idle lanes after every ply 765 / 769, every 2nd 941 / 980, 4th 1004 / 1058, 8th 1053 / 1129
+// (a lane whose game has ended sits out the plies up to the next look); refills for at least 4 idle lanes 1156 / 1429,
+// 6: 1164 / 1485, 8: 1170 / 1500, 12: 1167 / 1478; blocks of 448 threads 1163 / 1434, of 128 threads (three per SM) slower.
+#ifndef MCTSNC_GOMOKU_REFILL_MIN
+#define MCTSNC_GOMOKU_REFILL_MIN 8
+#endif
+constexpr int REFILL_MIN = MCTSNC_GOMOKU_REFILL_MIN;
+#ifndef MCTSNC_GOMOKU_PLIES_PER_LOOK
+#define MCTSNC_GOMOKU_PLIES_PER_LOOK 8
+#endif
+constexpr int PLIES_PER_LOOK = MCTSNC_GOMOKU_PLIES_PER_LOOK;   // plies between two looks at whether lanes are idle
+#ifndef MCTSNC_GOMOKU_THREADS
+#define MCTSNC_GOMOKU_THREADS 224
+#endif
+constexpr int DYN_THREADS = MCTSNC_GOMOKU_THREADS;
+// per warp: the parent position and, behind it, the ranks of the children that are played out (one byte each)
+constexpr int WARP_ACTIVE = TPL_WORDS, WARP_WORDS = TPL_WORDS + 60;
+constexpr size_t DYN_SMEM_BYTES = sizeof(unsigned) * ((size_t)THREAD_WORDS * DYN_THREADS + (size_t)WARP_WORDS * (DYN_THREADS / 32)) + FIVE_BYTES;
+static_assert((THREAD_WORDS * DYN_THREADS) % 4 == 0 && WARP_WORDS % 4 == 0 && TPL_LINES % 4 == 0, "16-byte loads of the warp's copy");
 
 template <bool OCP>
 __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Params p, int total_trees) {
-    extern __shared__ unsigned s_mem[];
+    extern __shared__ __align__(16) unsigned s_mem[];
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int P = p.n_playouts;
     int log2p = 0;
     while ((1 << log2p) < P) log2p++;
     unsigned *my = s_mem + tid;                                                     // word k of this thread: my[k * DYN_THREADS]
-    unsigned *tpl = s_mem + THREAD_WORDS * DYN_THREADS + warp * THREAD_WORDS;       // this warp's parent template
-    unsigned char *tpl_bytes = reinterpret_cast<unsigned char *>(tpl);
-    unsigned *s_five = s_mem + THREAD_WORDS * (DYN_THREADS + DYN_THREADS / 32);      // FIVE_WORDS words
-    uint2 *s_rows = reinterpret_cast<uint2 *>(s_five + FIVE_WORDS);                 // M pairs of window masks
-    for (int wd = tid; wd < FIVE_WORDS; wd += DYN_THREADS) {
-        unsigned bits = 0;
-        for (int b = 0; b < 32; b++) {
-            const unsigned window = (unsigned)(wd * 32 + b);
-            int above = 0, below = 0;
-            while (above < 5 && ((window >> (6 + above)) & 1u)) above++;
-            while (below < 5 && ((window >> (4 - below)) & 1u)) below++;
-            if (above + below == 4) bits |= 1u << b;
-        }
-        s_five[wd] = bits;
-    }
-    if (tid < M) {
-        // window cell 5 + k is the cell k rows down the line for the vertical and the diagonal, k rows UP for the
-        // anti-diagonal (whose cells are gathered the other way round); cells on rows outside the board do not exist
-        const int up = tid < 5 ? tid : 5, dn = M - 1 - tid < 5 ? M - 1 - tid : 5;
-        const unsigned span = (1u << (up + dn + 1)) - 1u;
-        s_rows[tid] = make_uint2(span << (15 - up), span << (15 - dn));
+    unsigned *tpl = s_mem + THREAD_WORDS * DYN_THREADS + warp * WARP_WORDS;         // this warp's copy of the parent position
+    const unsigned char *tpl_bytes = reinterpret_cast<const unsigned char *>(tpl + TPL_LIST);
+    unsigned char *act_bytes = reinterpret_cast<unsigned char *>(tpl + WARP_ACTIVE);
+    unsigned char *s_five = reinterpret_cast<unsigned char *>(s_mem + THREAD_WORDS * DYN_THREADS + WARP_WORDS * (DYN_THREADS / 32));
+    for (int window = tid; window < FIVE_BYTES; window += DYN_THREADS) {
+        int above = 0, below = 0;
+        while (above < 5 && ((window >> (6 + above)) & 1)) above++;
+        while (below < 5 && ((window >> (4 - below)) & 1)) below++;
+        s_five[window] = above + below == 4 ? 1 : 0;
     }
     __syncthreads();
     int tree = p.tree_base + (int)(((long long)blockIdx.x * (DYN_THREADS / 32) + warp) % total_trees);
@@ -620,50 +684,32 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
     // per-lane game (a lane may still be playing a game of an earlier tree after the warp has moved on)
     bool playing = false;
     int count = 0, turn = 0, action = 0, node = 0, my_tree = 0, my_start_turn = 0;
+    int ord = 0;              // the draw of the ply to come, already turned into a position of the list
+    int next_cell = 0, next_last = 0;   // list entries at that position and at the end of the list
+    float count_2m64 = 0.f;   // count * 2^-64, the factor of the draws scaled by 2^64
     long long rng_idx = 0;
     unsigned long long s0 = 0, s1 = 0, start0 = 0, start1 = 0;
     unsigned plies = 0;
     for (;;) {
         if (!have_tpl) {
-            // ---- describe the tree's step; build the parent template (warp-cooperative)
+            // ---- describe the tree's step; fetch the parent position
             const StepInfo si = p.step[tree];
             mode = si.mode;
             n_items = si.n_active << log2p;
             selected = si.selected;
             first_child = si.first_child;
             sel_turn = g_turn(si.sel_meta);
-            exhausted = n_items == 0 || *(volatile int *)&p.step[tree].game_counter >= n_items;
+            count0 = si.n_empty;
+            int taken = 0;   // read by one lane, so that the whole warp sees the same value
+            if (lane == 0) taken = *(volatile int *)&p.step[tree].game_counter;
+            taken = __shfl_sync(0xFFFFFFFFu, taken, 0);
+            exhausted = n_items == 0 || taken >= n_items;
             if (!exhausted) {
-                const unsigned *nb = p.board + ((long long)tree * p.cap + selected) * 16;
-                unsigned neg[WORDS], pos[WORDS];
-                int prefix[WORDS + 1];
-                int acc = 0;
-#pragma unroll
-                for (int w = 0; w < WORDS; w++) {
-                    neg[w] = nb[w];
-                    pos[w] = nb[8 + w];
-                    prefix[w] = acc;
-                    acc += __popc(~(neg[w] | pos[w]) & (w == 7 ? 0x1u : 0xFFFFFFFFu));
-                }
-                prefix[WORDS] = acc;
-                count0 = acc;
-                for (int w = lane; w < LIST_WORDS; w += 32) tpl[w] = 0;
-                __syncwarp();
-#pragma unroll
-                for (int w = 0; w < WORDS; w++) {   // lane handles cell 32 * w + lane
-                    const int c = 32 * w + lane;
-                    const unsigned empty = ~(neg[w] | pos[w]);
-                    if (c < A && ((empty >> lane) & 1u)) tpl_bytes[prefix[w] + __popc(empty & ((1u << lane) - 1u))] = (unsigned char)c;
-                }
-                if (lane < M) {
-                    unsigned row = 0;
-                    for (int j = 0; j < N; j++) {
-                        const int c = lane * N + j;
-                        if ((neg[c >> 5] >> (c & 31)) & 1u) row |= 1u << j;
-                        if ((pos[c >> 5] >> (c & 31)) & 1u) row |= 1u << (16 + j);
-                    }
-                    tpl[LIST_WORDS + lane] = row;
-                }
+                __syncwarp();   // lanes of an earlier refill are done with the copy
+                const unsigned *src = p.tpl + (long long)tree * TPL_WORDS;
+                for (int w = lane; w < TPL_WORDS; w += 32) tpl[w] = src[w];
+                const unsigned char *ranks = p.active_rank + tree * A;
+                for (int k = lane; k < si.n_active; k += 32) act_bytes[k] = ranks[k];
                 __syncwarp();
             }
             have_tpl = true;
@@ -681,47 +727,79 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
             if (!playing && item < n_items) {
                 const int t = item & (P - 1);
                 int skip = 1 << 30;   // position of the parent's list that the child's list leaves out
-                unsigned stone_row = 0xFFFFFFFFu, stone_bit = 0;
+                int cell = 0;
                 if (mode == MODE_ALL_CHILDREN) {
-                    const int rank = p.active_rank[tree * A + (item >> log2p)];
-                    action = tpl_bytes[rank];            // children are the first empty cells in ascending order
+                    const int rank = act_bytes[item >> log2p];
+                    cell = tpl_bytes[rank];              // children are the first empty cells in ascending order
+                    action = (cell >> 4) * N + (cell & 15);
                     skip = rank;
                     node = first_child + rank;
                     count = count0 - 1;
                     turn = -sel_turn;
-                    const int i = (action * 137) >> 11;
-                    stone_row = (unsigned)i;
-                    stone_bit = 1u << ((sel_turn > 0 ? 16 : 0) + (action - i * N));
                 } else {   // the selected node itself is played out, with the streams of action 0
                     action = 0;
                     node = selected;
                     count = count0;
                     turn = sel_turn;
                 }
-                // the child's list: the parent's without position `skip`
+                rng_idx = OCP ? ((long long)tree * P + t) : (((long long)tree * A + action) * P + t);
+                const ulonglong2 rs = p.rng_playout[rng_idx];   // on its way while the position is copied
+                // the child's list: the parent's without position `skip`.  Four words at a time; a word behind the one that
+                // holds `skip` takes its bytes one position further up (a funnel shift by 0 or 8 bits), the word that holds
+                // it is put right afterwards.  Words past the last entry are never read; up to three words past the list
+                // are written and then covered by the lines.
                 const int skip_word = skip >> 2;
-                unsigned prev = tpl[0];
-                for (int w = 0; w < LIST_WORDS; w++) {
-                    const unsigned next = w + 1 < LIST_WORDS ? tpl[w + 1] : 0u;
-                    unsigned out = prev;
-                    if (w >= skip_word) {
-                        const unsigned shifted = __funnelshift_r(prev, next, 8);
-                        if (w > skip_word) out = shifted;
-                        else {
-                            const unsigned keep = (1u << (8 * (skip & 3))) - 1u;
-                            out = (prev & keep) | (shifted & ~keep);
-                        }
-                    }
-                    my[w * DYN_THREADS] = out;
-                    prev = next;
+                const int chunks = (count0 + 15) >> 4;
+                const uint4 *tpl_list4 = reinterpret_cast<const uint4 *>(tpl + TPL_LIST);
+                uint4 v = tpl_list4[0];
+                for (int c = 0; c < chunks; c++) {
+                    const uint4 nx = tpl_list4[c + 1];   // c + 1 <= 15: the lines follow the list in the warp's copy
+                    const int d = skip_word - 4 * c;
+                    unsigned *dst = my + 4 * c * DYN_THREADS;
+                    dst[0 * DYN_THREADS] = __funnelshift_r(v.x, v.y, d < 0 ? 8 : 0);
+                    dst[1 * DYN_THREADS] = __funnelshift_r(v.y, v.z, d < 1 ? 8 : 0);
+                    dst[2 * DYN_THREADS] = __funnelshift_r(v.z, v.w, d < 2 ? 8 : 0);
+                    dst[3 * DYN_THREADS] = __funnelshift_r(v.w, nx.x, d < 3 ? 8 : 0);
+                    v = nx;
                 }
-                for (int i = 0; i < M; i++) my[(LIST_WORDS + i) * DYN_THREADS] = tpl[LIST_WORDS + i] | ((unsigned)i == stone_row ? stone_bit : 0u);
+                if (skip_word < LIST_WORDS) {
+                    const unsigned prev = tpl[TPL_LIST + skip_word], next = tpl[TPL_LIST + skip_word + 1];
+                    const unsigned keep = (1u << (8 * (skip & 3))) - 1u;
+                    my[skip_word * DYN_THREADS] = (prev & keep) | (__funnelshift_r(prev, next, 8) & ~keep);
+                }
+                const uint4 *tpl_lines4 = reinterpret_cast<const uint4 *>(tpl + TPL_LINES);
+#pragma unroll
+                for (int c = 0; c < LINE_WORDS / 4; c++) {
+                    const uint4 l = tpl_lines4[c];
+                    unsigned *dst = my + (LIST_WORDS + 4 * c) * DYN_THREADS;
+                    dst[0 * DYN_THREADS] = l.x;
+                    dst[1 * DYN_THREADS] = l.y;
+                    dst[2 * DYN_THREADS] = l.z;
+                    dst[3 * DYN_THREADS] = l.w;
+                }
+                static_assert(LINE_WORDS % 4 == 2, "the last two line words");
+                my[(LIST_WORDS + LINE_WORDS - 2) * DYN_THREADS] = tpl[TPL_LINES + LINE_WORDS - 2];
+                my[(LIST_WORDS + LINE_WORDS - 1) * DYN_THREADS] = tpl[TPL_LINES + LINE_WORDS - 1];
+                if (mode == MODE_ALL_CHILDREN) {   // the child's own stone, put down by the side to move at the parent
+                    const int i = cell >> 4, j = cell & 15;
+                    const int hs = sel_turn > 0 ? 16 : 0;
+                    my[(LINE_ROW + i) * DYN_THREADS] |= 1u << (hs + j);
+                    my[(LINE_COL + j) * DYN_THREADS] |= 1u << (hs + i);
+                    my[(LINE_DIAG + ((i - j + 14) & 15)) * DYN_THREADS] |= 1u << (hs + j);
+                    my[(LINE_ANTI + ((i + j) & 15)) * DYN_THREADS] |= 1u << (hs + j);
+                }
+                count_2m64 = (float)count * RNG_2M64;
                 my_tree = tree;
                 my_start_turn = turn;
-                rng_idx = OCP ? ((long long)tree * P + t) : (((long long)tree * A + action) * P + t);
-                const ulonglong2 rs = p.rng_playout[rng_idx];
                 s0 = start0 = rs.x;
                 s1 = start1 = rs.y;
+                ord = __float2int_rz(__fmul_rn(rng_uniform_times_2p64(s0, s1), count_2m64));   // the draw of the first ply
+                {
+                    const unsigned char *list = reinterpret_cast<const unsigned char *>(my);
+                    const int q_last = max(count - 1, 0);
+                    next_last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
+                    next_cell = list[((ord >> 2) * DYN_THREADS) * 4 + (ord & 3)];
+                }
                 plies = 0;
                 playing = true;
             }
@@ -738,17 +816,22 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
             }
             if (__ballot_sync(0xFFFFFFFFu, playing) == 0u) break;
         }
-        if (playing) {
-            // ---- one ply
-            const float u = rng_uniform_f32(s0, s1);
-            const float prod = __fmul_rn(u, (float)count);   // float32 * int16 -> float32 (:2061)
-            const int ord = __float2int_rz(prod);
+#pragma unroll
+        for (int rep = 0; rep < PLIES_PER_LOOK; rep++) {
+          if (playing) {
+            // ---- one ply (src/mctsnc.py:2059-2064).  float32 u * int16 count -> float32 (:2061); here (u * 2^64) * (count * 2^-64):
+            // the same product, rounded once.  u == 1.0f gives ord == count.  The draw of a ply is made one ply ahead, next to
+            // the work of the ply before it, so that the chain of dependent steps of a ply starts at the list; if the game ends
+            // with this ply, the stream is stored as it was before the draw for the next one.
+            const int this_ord = ord;
+            unsigned long long end0 = s0, end1 = s1;   // the stream after the draw of this ply
+            ord = __float2int_rz(__fmul_rn(rng_uniform_times_2p64(s0, s1), count_2m64 - RNG_2M64));
             int outcome = 2;
-            if (ord >= count) {
+            if (this_ord >= count) {
                 // u == 1.0f: replay this game through the byte-level emulation of the reference
                 const EmuResult er = playout_emulated(p.board + ((long long)my_tree * p.cap + node) * 16, my_start_turn, start0, start1);
-                s0 = er.s0;
-                s1 = er.s1;
+                end0 = er.s0;
+                end1 = er.s1;
                 outcome = er.outcome;
                 plies = er.plies;
                 TreeState *st = p.state + my_tree;
@@ -756,99 +839,51 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 atomicOr(&st->status, STATUS_UB_DRAW | (er.err ? STATUS_INTERNAL : 0u));
             } else {
                 // last_action = legal[ord]; legal[ord] = legal[count - 1]; count -= 1   (:2062, :215-217).  List entry q of this
-                // thread is byte q & 3 of its word q >> 2: byte loads and stores, no read-modify-write of words
+                // thread is byte q & 3 of its word q >> 2: byte loads and stores, no read-modify-write of words.  The two
+                // entries a ply reads were fetched at the end of the ply before (after its store); here the two of the next
+                // ply are fetched, so that they arrive while this ply's stone is tested.
                 unsigned char *list = reinterpret_cast<unsigned char *>(my);
-                const int q_last = count - 1;
-                const unsigned char last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
-                unsigned char *at_ord = list + ((ord >> 2) * DYN_THREADS) * 4 + (ord & 3);
-                const int a = *at_ord;
-                *at_ord = last;
+                const int cell = next_cell;
+                list[((this_ord >> 2) * DYN_THREADS) * 4 + (this_ord & 3)] = (unsigned char)next_last;
                 count--;
-                const int i = (a * 137) >> 11;   // a / 15 for a < 225
-                const int j = a - i * N;
+                count_2m64 -= RNG_2M64;   // exact: small integers times 2^-64
+                const int q_last = max(count - 1, 0);
+                next_last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
+                next_cell = list[((ord >> 2) * DYN_THREADS) * 4 + (ord & 3)];   // ord <= count <= 225: inside the list words
+                const int i = cell >> 4, j = cell & 15;
                 const int hs = turn > 0 ? 16 : 0;
-                const unsigned row = my[(LIST_WORDS + i) * DYN_THREADS] | (1u << (hs + j));
-                my[(LIST_WORDS + i) * DYN_THREADS] = row;
                 plies++;
-                // compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) without data-dependent loops: for each of the
-                // four directions the mover's stones on the line through (i, j) are gathered into a window with the new
-                // stone at bit 15 and the cell r steps down the line at bit 15 + r (15 - r for the anti-diagonal), five cells
-                // either way; a table with one bit per window then says whether the stones next to bit 15 add up to exactly
-                // 4, which is what the reference asks for (it counts at most 5 stones either way and wants a total of 4).
-                // The row words of the five rows above and below are rotated so that column j sits at bit 15: the vertical
-                // line takes bit 15 of each, the two diagonals bits 15 - r and 15 + r, which are collected for the rows above
-                // (x) and below (y) separately and sorted into the two windows afterwards.  Rows outside the board are read
-                // all the same (this thread's list words, or row 14 again) and masked out of the windows.
-                bool win;
-                {
-                    const unsigned *my_row = my + (LIST_WORDS + i) * DYN_THREADS;
-                    // column c of the mover's half of a row word goes to bit 15 + c - j: one rotation, by 17 + j for the
-                    // half at bits 0..14 (a left shift by 15 - j) and by 1 + j for the half at bits 16..30; the 15 masked
-                    // bits never wrap around
-                    const unsigned half = 0x7FFFu << hs;
-                    const int rot = (17 + j + hs) & 31;
-                    const unsigned gh = __funnelshift_r(row & half, row & half, rot);
-#if MCTSNC_GOMOKU_FIVE_TABLE
-                    unsigned gv = 0, x = 0, y = 0;
-#pragma unroll
-                    for (int r = 1; r <= 5; r++) {
-                        const unsigned both = (1u << (15 - r)) | (1u << (15 + r));
-                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;                      // row i - r
-                        const unsigned up = __funnelshift_r(up_w, up_w, rot);
-                        gv |= (up >> r) & (1u << (15 - r));
-                        x |= up & both;                                                            // (i - r, j - r), (i - r, j + r)
-                        const int rd = min(i + r, M - 1);                                          // row i + r
-                        const unsigned dn_w = my[(LIST_WORDS + rd) * DYN_THREADS] & half;
-                        const unsigned dn = __funnelshift_r(dn_w, dn_w, rot);
-                        gv |= (dn << r) & (1u << (15 + r));
-                        y |= dn & both;                                                            // (i + r, j + r), (i + r, j - r)
-                    }
-                    const uint2 exists = s_rows[i];
-                    const unsigned below15 = 0x7C00u, above15 = 0x1F0000u;                         // bits 10..14, 16..20
-                    const unsigned gd = ((x & below15) | (y & above15)) & exists.x;                // (i - r, j - r) .. (i + r, j + r)
-                    const unsigned ga = ((x & above15) | (y & below15)) & exists.y;                // (i - r, j + r) .. (i + r, j - r)
-                    gv &= exists.x;
-                    const unsigned wh = (gh >> 10) & 0x7FFu, wv = (gv >> 10) & 0x7FFu, wd = (gd >> 10) & 0x7FFu, wa = (ga >> 10) & 0x7FFu;
-                    win = (((s_five[wh >> 5] >> (wh & 31)) | (s_five[wv >> 5] >> (wv & 31)) | (s_five[wd >> 5] >> (wd & 31)) |
-                            (s_five[wa >> 5] >> (wa & 31))) & 1u) != 0;
-#else
-                    // the runs of stones next to bit 15 are counted with find-first-set / count-leading-zeros; rows outside
-                    // the board are not masked when read, a run is cut to the rows that exist on its side instead
-                    unsigned gv = 0, x = 0, y = 0;
-#pragma unroll
-                    for (int r = 1; r <= 5; r++) {
-                        const unsigned both = (1u << (15 - r)) | (1u << (15 + r));
-                        const unsigned up_w = my_row[-r * DYN_THREADS] & half;                      // row i - r
-                        const unsigned up = __funnelshift_r(up_w, up_w, rot);
-                        gv |= (up >> r) & (1u << (15 - r));
-                        x |= up & both;                                                            // (i - r, j - r), (i - r, j + r)
-                        const int rd = min(i + r, M - 1);                                          // row i + r
-                        const unsigned dn_w = my[(LIST_WORDS + rd) * DYN_THREADS] & half;
-                        const unsigned dn = __funnelshift_r(dn_w, dn_w, rot);
-                        gv |= (dn << r) & (1u << (15 + r));
-                        y |= dn & both;                                                            // (i + r, j + r), (i + r, j - r)
-                    }
-                    const unsigned below15 = 0x7C00u, above15 = 0x1F0000u;                         // bits 10..14, 16..20
-                    const unsigned gd = (x & below15) | (y & above15);                             // (i - r, j - r) .. (i + r, j + r)
-                    const unsigned ga = (x & above15) | (y & below15);                             // (i - r, j + r) .. (i + r, j - r)
-                    const int rows_up = i, rows_dn = M - 1 - i;
-                    const int h_hi = __ffs(~(gh >> 16)) - 1, h_lo = __clz(~(gh << 17));
-                    const int v_hi = min(__ffs(~(gv >> 16)) - 1, rows_dn), v_lo = min(__clz(~(gv << 17)), rows_up);
-                    const int d_hi = min(__ffs(~(gd >> 16)) - 1, rows_dn), d_lo = min(__clz(~(gd << 17)), rows_up);
-                    const int a_hi = min(__ffs(~(ga >> 16)) - 1, rows_up), a_lo = min(__clz(~(ga << 17)), rows_dn);
-                    win = (h_hi + h_lo == 4) | (v_hi + v_lo == 4) | (d_hi + d_lo == 4) | (a_hi + a_lo == 4);
-#endif
-                }
+                // compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) without loops: the stone goes into the word of
+                // its row, column, diagonal and anti-diagonal; of each word the mover's half is rotated so that the new
+                // stone sits at bit 5, and the 11 bits around it index the table.  The bits of the half never wrap into the
+                // window: rotating right by s = hs + pos - 5, a bit b < s lands at 32 - s + b >= 23 (low half: s <= 9; high
+                // half: b >= 16, s <= 25), and a negative s is a shift of the low half to the left by at most 5.
+                const unsigned half = 0x7FFFu << hs;
+                const unsigned bit_j = 1u << (hs + j), bit_i = 1u << (hs + i);
+                const int rot_j = hs + j - 5, rot_i = hs + i - 5;   // the funnel shift takes them modulo 32
+                unsigned *row_w = my + (LINE_ROW + i) * DYN_THREADS;
+                unsigned *col_w = my + (LINE_COL + j) * DYN_THREADS;
+                unsigned *diag_w = my + (LINE_DIAG + ((i - j + 14) & 15)) * DYN_THREADS;
+                unsigned *anti_w = my + (LINE_ANTI + ((i + j) & 15)) * DYN_THREADS;
+                const unsigned wr = *row_w | bit_j, wc = *col_w | bit_i, wd = *diag_w | bit_j, wa = *anti_w | bit_j;
+                *row_w = wr;
+                *col_w = wc;
+                *diag_w = wd;
+                *anti_w = wa;
+                const unsigned tr = wr & half, tc = wc & half, td = wd & half, ta = wa & half;
+                const unsigned win = s_five[__funnelshift_r(tr, tr, rot_j) & 0x7FFu] | s_five[__funnelshift_r(tc, tc, rot_i) & 0x7FFu] |
+                                     s_five[__funnelshift_r(td, td, rot_j) & 0x7FFu] | s_five[__funnelshift_r(ta, ta, rot_j) & 0x7FFu];
                 if (win) outcome = turn;
                 else if (count == 0) outcome = 0;
                 turn = -turn;
             }
             if (outcome != 2) {
-                p.rng_playout[rng_idx] = make_ulonglong2(s0, s1);
+                p.rng_playout[rng_idx] = make_ulonglong2(end0, end1);
                 if (outcome != 0) atomicAdd(&p.child_out[(my_tree * A + action) * 2 + (outcome > 0 ? 1 : 0)], 1);
                 atomicAdd(&p.state[my_tree].plies, (unsigned long long)plies);
                 playing = false;
             }
+          }
         }
     }
 }

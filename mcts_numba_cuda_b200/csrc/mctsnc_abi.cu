@@ -92,6 +92,7 @@ struct mctsnc_handle {
     // Gomoku only
     unsigned *gboard = nullptr;           // [trees][cap][16]
     gomoku::StepInfo *gstep = nullptr;    // [trees]
+    unsigned *gtpl = nullptr;             // [trees][gomoku::TPL_WORDS]
     int *path_ns = nullptr, *path_wins = nullptr;
     signed char *child_outcome = nullptr;
     unsigned char *child_action = nullptr;
@@ -525,6 +526,7 @@ void release(mctsnc_handle *h) {
     cudaFree(h->trace_count);
     cudaFree(h->gboard);
     cudaFree(h->gstep);
+    cudaFree(h->gtpl);
     cudaFree(h->path_ns);
     cudaFree(h->path_wins);
     cudaFree(h->child_outcome);
@@ -657,6 +659,7 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
     p.child_outcome = h->child_outcome;
     p.child_action = h->child_action;
     p.active_rank = h->active_rank;
+    p.tpl = h->gtpl;
     p.rng_playout = h->rng_playout;
     p.rng_expand = h->rng_expand;
     p.root_board = h->root_gboard;
@@ -905,7 +908,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     h->rng_per_search = ocp ? (long long)c.n_trees * c.n_playouts : (long long)c.n_trees * h->A * c.n_playouts;
     h->dyn_smem = sizeof(ulonglong2) * (size_t)(h->rng_per_search / c.n_trees);
     if (is_gomoku(c))   // per-thread game state + per-warp templates + the tables of the exactly-five test
-        h->dyn_smem = sizeof(unsigned) * ((size_t)gomoku::THREAD_WORDS * (gomoku::DYN_THREADS + gomoku::DYN_THREADS / 32) + gomoku::TABLE_WORDS);
+        h->dyn_smem = gomoku::DYN_SMEM_BYTES;
     if (h->dyn_smem > 48 * 1024) {
         const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>)
                                           : search_kernel_ptr(c);
@@ -920,6 +923,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc && !is_gomoku(c)) rc = dev_alloc(h, &h->board, nodes);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->gboard, nodes * 16);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->gstep, h->n_trees_total);
+    if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->gtpl, h->n_trees_total * gomoku::TPL_WORDS);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->path_ns, h->n_trees_total * PATH_CAP);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->path_wins, h->n_trees_total * PATH_CAP);
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->child_outcome, h->n_trees_total * h->A);
@@ -928,6 +932,7 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (!rc && is_gomoku(c)) rc = dev_alloc(h, &h->root_gboard, (long long)c.max_batch * 16);
     if (!rc && is_gomoku(c) && cudaMallocHost((void **)&h->h_root_gboard, sizeof(unsigned) * 16 * c.max_batch) != cudaSuccess) rc = MCTSNC_E_NO_MEMORY;
     if (!rc && is_gomoku(c)) rc = (int)cudaMemset(h->gstep, 0, sizeof(gomoku::StepInfo) * h->n_trees_total);
+    if (!rc && is_gomoku(c)) rc = (int)cudaMemset(h->gtpl, 0, sizeof(unsigned) * gomoku::TPL_WORDS * h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->parent, nodes);
     if (!rc) rc = dev_alloc(h, &h->state, h->n_trees_total);
     if (!rc) rc = dev_alloc(h, &h->paths, h->n_trees_total * PATH_CAP);
