@@ -13,6 +13,8 @@
 // Position encoding: column c of the 6x7 board owns bits 7c .. 7c+5 (bit 7c = bottom cell) and a guard bit 7c+6 that
 // stays 0, so that shifts by 1, 6, 7, 8 test the four line directions without wrapping between columns.
 #pragma once
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "rng.cuh"
 
@@ -188,7 +190,8 @@ struct __align__(16) GameSlot {
 
 struct Shared {
     GameSlot slot[A];        // children that need real playouts, in expansion order
-    int tally[A][2];         // per slot: games won by -1, by +1
+    int tally[A][2];         // per slot: games won by -1, by +1 (of the games this block played)
+    int gather[A][2];        // cluster of blocks per tree: the sums over the blocks, kept by the first block
     int path[48];
     int path_ns[48];
     int path_wins[48];
@@ -226,24 +229,41 @@ struct Shared {
 // `n_steps` steps of tree g by the whole block, from the state the tree has in global memory and back to it.
 // The random streams of the tree (ACP: 7*P, OCP: P states of 16 B) stay in dynamic shared memory meanwhile: they are
 // read at the start of every game and written back at its end, by one thread each.
-template <bool OCP>
+//
+// CL > 1: a thread-block cluster of CL blocks grows the tree (launches with so few trees that a tree would otherwise be
+// bound by what one SM can play per step).  The first block of the cluster walks, expands and backs up as before and
+// hands the step's games (slots) to the shared memory of the others; every block plays the games of P / CL of the P
+// playout indices of every child -- it keeps the streams of exactly those in its shared memory -- and adds its tallies
+// to the first block's `gather`.  Two cluster barriers per step; all blocks run the same loop, so every block reaches
+// every barrier.
+template <bool OCP, int CL>
 __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulonglong2 *s_rng, const int g, const int n_steps,
                                           const bool first) {
+    namespace cg = cooperative_groups;
+    static_assert(CL == 1 || CL == 2 || CL == 4 || CL == 8, "cluster sizes");
+    constexpr int LOG_CL = CL == 8 ? 3 : (CL == 4 ? 2 : (CL == 2 ? 1 : 0));
     const int tid = threadIdx.x;
     const int nt = blockDim.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const int P = p.n_playouts;
+    const int rank = CL > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int log2_local = p.log2_playouts - LOG_CL;   // this block plays P_local = P / CL playout indices of every child
+    const int P_local = P >> LOG_CL;
     int4 *rec = p.rec + (long long)g * p.cap;
     ulonglong2 *board = p.board + (long long)g * p.cap;
     int *parent = p.parent + (long long)g * p.cap;
     TreeState *st = p.state + g;
     const bool thrifty = (p.variant == 0 || p.variant == 2);
+    const bool walker = warp == 0 && rank == 0;   // the warp that selects, expands and backs up
 
     const int n_streams = OCP ? P : A * P;
     ulonglong2 *g_rng = p.rng_playout + (long long)g * n_streams;
-    for (int i = tid; i < n_streams; i += nt) s_rng[i] = g_rng[i];
-    if (tid == 0) {
+    // stream (action, t) of the tree sits at local index action * P_local + (t - rank * P_local)
+    for (int i = tid; i < (n_streams >> LOG_CL); i += nt)
+        s_rng[i] = g_rng[((i >> log2_local) << p.log2_playouts) + rank * P_local + (i & (P_local - 1))];
+    if (CL > 1 && tid < 2 * A) s.tally[tid >> 1][tid & 1] = 0;
+    if (tid == 0 && rank == 0) {
         const int b = g / p.n_trees;
         if (first) {
             const int turn = p.root_turn[b];
@@ -277,14 +297,96 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         }
         for (int a = 0; a < A + 2; a++) s.ae[a] = p.actions_expanded[g * (A + 2) + a];
     }
-    __syncthreads();
+    if (CL > 1) cg::this_cluster().sync();
+    else __syncthreads();
 
     const double c_ucb = (double)p.ucb_c;
     unsigned my_plies = 0, my_ub = 0, my_err = 0;
 
-    for (int step = 0; step < n_steps; step++) {
-        // =========================================================== select + expand (warp 0)
-        if (warp == 0) {
+    // The walker warp runs steps on its own for as long as they select a terminal node (nothing to play: the backup follows
+    // at once) and meets the other threads only for a step with games, or when the steps are done (MODE_DONE).
+    int step = 0;
+    bool backup_due = false;   // the walker's: the step it selected last has not been backed up yet
+    for (;;) {
+        // =========================================================== backup of the step before, select + expand (warp 0)
+        if (walker) for (;;) {
+            if (backup_due) {
+                // ======================================================= backup (_backup_* of the reference)
+                __syncwarp();
+                const unsigned c_backup = (unsigned)clock();
+                const int (*tally)[2] = CL > 1 ? s.gather : s.tally;
+                const int mode = s.mode;
+                const int n_exp = s.n_exp;
+                const int sel_meta = s.sel_meta;
+                const int child_turn = -meta_turn(sel_meta);
+                int neg_tot = 0, pos_tot = 0;
+                long long n_tot = P;
+                if (mode == MODE_ALL_CHILDREN) {
+                    int my_neg = 0, my_pos = 0;
+                    if (lane < n_exp) {
+                        const int o = s.child_outcome[lane];
+                        const int j = s.child_slot[lane];
+                        const bool played = !OCP || lane == s.pick;
+                        if (j >= 0) {
+                            my_neg = tally[j][0];
+                            my_pos = tally[j][1];
+                        } else if (played) {
+                            // a terminal child: its stored outcome stands for all P playouts (src/mctsnc.py:2016-2021)
+                            my_neg = o == -1 ? P : 0;
+                            my_pos = o == 1 ? P : 0;
+                        }
+                        // children start from ns = ns_wins = 0 (src/mctsnc.py:1819-1820), then _backup_1_acp_* / the
+                        // thread-0 part of _backup_ocp credit them (:2172-2177, :2104-2114)
+                        const int cns = played ? P : 0;
+                        const int cw = played ? (child_turn == 1 ? my_neg : my_pos) : 0;
+                        rec[s.first_child + lane] =
+                            make_int4(cns, cw, -1, make_meta(0, o != 2, o, child_turn, meta_depth(sel_meta) + 1));
+                        if (!OCP) {
+                            s.child_out[s.child_action[lane]][0] = my_neg;
+                            s.child_out[s.child_action[lane]][1] = my_pos;
+                        }
+                    }
+                    neg_tot = __reduce_add_sync(0xFFFFFFFFu, my_neg);
+                    pos_tot = __reduce_add_sync(0xFFFFFFFFu, my_pos);
+                    if (!OCP) n_tot = (long long)P * n_exp;
+                } else if (mode == MODE_TERMINAL) {
+                    neg_tot = s.out_neg;
+                    pos_tot = s.out_pos;
+                } else {
+                    neg_tot = tally[0][0];
+                    pos_tot = tally[0][1];
+                    if (!OCP && lane == 0) {
+                        s.child_out[0][0] = neg_tot;
+                        s.child_out[0][1] = pos_tot;
+                    }
+                }
+                const int plen = s.path_len;
+                for (int e = lane; e < plen; e += 32) {
+                    const int node = s.path[e];
+                    const int turn_e = (e & 1) ? -s.root_turn : s.root_turn;
+                    const int ns = s.path_ns[e] + (int)n_tot;
+                    const int wins = s.path_wins[e] + (turn_e == 1 ? neg_tot : pos_tot);
+                    if (e == plen - 1 && mode == MODE_ALL_CHILDREN) {
+                        rec[node] = make_int4(ns, wins, s.first_child, sel_meta | s.exp_mask);
+                    } else {
+                        *reinterpret_cast<int2 *>(&rec[node]) = make_int2(ns, wins);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    s.out_neg = neg_tot;
+                    s.out_pos = pos_tot;
+                    s.stage_cycles[2] += c_backup - s.stage_mark;
+                    s.stage_cycles[3] += (unsigned)clock() - c_backup;
+                }
+                __syncwarp();
+                backup_due = false;
+            }
+            if (step == n_steps) {
+                if (lane == 0) s.mode = MODE_DONE;
+                if (CL > 1 && lane > 0 && lane < CL) cg::this_cluster().map_shared_rank(&s, lane)->mode = MODE_DONE;
+                break;
+            }
             const unsigned c_step = (unsigned)clock();   // 32-bit cycle counts: differences are right modulo 2^32
             int node = 0;
             int4 r = rec[0];
@@ -410,6 +512,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                             s.slot[j] = gs;
                             s.tally[j][0] = 0;
                             s.tally[j][1] = 0;
+                            s.gather[j][0] = 0;
+                            s.gather[j][1] = 0;
                         }
                     }
                 } else {
@@ -427,6 +531,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         s.slot[0] = gs;
                         s.tally[0][0] = 0;
                         s.tally[0][1] = 0;
+                        s.gather[0][0] = 0;
+                        s.gather[0][1] = 0;
                     }
                 }
             }
@@ -464,8 +570,29 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 s.stage_cycles[1] += c_play - c_expand;
                 s.stage_mark = c_play;
             }
+            step++;
+            backup_due = true;
+            if (mode == MODE_TERMINAL) continue;
+            if (CL > 1) {
+                // the step's games for the other blocks of the cluster: stores into their shared memory, made visible by
+                // the barrier below
+                __syncwarp();
+                for (int other = 1; other < CL; other++) {
+                    Shared *rs = cg::this_cluster().map_shared_rank(&s, other);
+                    if (lane < n_slots) rs->slot[lane] = s.slot[lane];
+                    if (lane == 0) {
+                        rs->n_slots = n_slots;
+                        rs->mode = mode;
+                        rs->sel_meta = r.w;
+                        rs->next_item = 0;
+                    }
+                }
+            }
+            break;
         }
-        __syncthreads();
+        if (CL > 1) cg::this_cluster().sync();
+        else __syncthreads();
+        if (s.mode == MODE_DONE) break;
 
         // =========================================================== playouts (all threads)
         // Games are handed out one at a time from a counter in shared memory, so the threads of the block stay busy
@@ -479,7 +606,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         // guard bit once the column is full; top = all stones + BOTTOM_ROW).  A move in a column with room is then
         // top & (six cells of the column), and top + move puts the marker one cell up.
         {
-            const int n_items = s.n_slots << p.log2_playouts;
+            const int n_items = s.n_slots << log2_local;
             // the side to move in the played-out positions: the other side than at the selected node, unless the
             // selected node itself is played out
             const int first_mover = (s.mode == MODE_TREE_FULL) ? meta_turn(s.sel_meta) : -meta_turn(s.sel_meta);
@@ -489,7 +616,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             int rng_idx = 0, stones = 0, j = 0;
             int item = atomicAdd(&s.next_item, 1);
             if (item < n_items) {
-                j = item >> p.log2_playouts;
+                j = item >> log2_local;
                 const GameSlot gs = s.slot[j];
                 side_even = gs.cur;
                 side_odd = (gs.top - BOTTOM_ROW) ^ gs.cur;
@@ -497,7 +624,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 legal = gs.legal;
                 count = gs.count;
                 stones = gs.stones;
-                rng_idx = gs.rng_base + (item & (P - 1));
+                rng_idx = (gs.rng_base >> LOG_CL) + (item & (P_local - 1));
                 const ulonglong2 rs = s_rng[rng_idx];
                 s0 = rs.x;
                 s1 = rs.y;
@@ -564,7 +691,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                     if (winner != 0) atomicAdd(&s.tally[j][winner > 0 ? 1 : 0], 1);
                     item = atomicAdd(&s.next_item, 1);
                     if (item < n_items) {
-                        j = item >> p.log2_playouts;
+                        j = item >> log2_local;
                         const GameSlot gs = s.slot[j];
                         side_even = gs.cur;
                         side_odd = (gs.top - BOTTOM_ROW) ^ gs.cur;
@@ -572,7 +699,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         legal = gs.legal;
                         count = gs.count;
                         stones = gs.stones;
-                        rng_idx = gs.rng_base + (item & (P - 1));
+                        rng_idx = (gs.rng_base >> LOG_CL) + (item & (P_local - 1));
                         const ulonglong2 rs = s_rng[rng_idx];
                         s0 = rs.x;
                         s1 = rs.y;
@@ -580,88 +707,37 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 }
             }
         }
-        __syncthreads();
-
-        // =========================================================== backup (warp 0)
-        if (warp == 0) {
-            const unsigned c_backup = (unsigned)clock();
-            const int mode = s.mode;
-            const int n_exp = s.n_exp;
-            const int sel_meta = s.sel_meta;
-            const int child_turn = -meta_turn(sel_meta);
-            int neg_tot = 0, pos_tot = 0;
-            long long n_tot = P;
-            if (mode == MODE_ALL_CHILDREN) {
-                int my_neg = 0, my_pos = 0;
-                if (lane < n_exp) {
-                    const int o = s.child_outcome[lane];
-                    const int j = s.child_slot[lane];
-                    const bool played = !OCP || lane == s.pick;
-                    if (j >= 0) {
-                        my_neg = s.tally[j][0];
-                        my_pos = s.tally[j][1];
-                    } else if (played) {
-                        // a terminal child: its stored outcome stands for all P playouts (src/mctsnc.py:2016-2021)
-                        my_neg = o == -1 ? P : 0;
-                        my_pos = o == 1 ? P : 0;
-                    }
-                    // children start from ns = ns_wins = 0 (src/mctsnc.py:1819-1820), then _backup_1_acp_* / the
-                    // thread-0 part of _backup_ocp credit them (:2172-2177, :2104-2114)
-                    const int cns = played ? P : 0;
-                    const int cw = played ? (child_turn == 1 ? my_neg : my_pos) : 0;
-                    rec[s.first_child + lane] =
-                        make_int4(cns, cw, -1, make_meta(0, o != 2, o, child_turn, meta_depth(sel_meta) + 1));
-                    if (!OCP) {
-                        s.child_out[s.child_action[lane]][0] = my_neg;
-                        s.child_out[s.child_action[lane]][1] = my_pos;
-                    }
-                }
-                neg_tot = __reduce_add_sync(0xFFFFFFFFu, my_neg);
-                pos_tot = __reduce_add_sync(0xFFFFFFFFu, my_pos);
-                if (!OCP) n_tot = (long long)P * n_exp;
-            } else if (mode == MODE_TERMINAL) {
-                neg_tot = s.out_neg;
-                pos_tot = s.out_pos;
-            } else {
-                neg_tot = s.tally[0][0];
-                pos_tot = s.tally[0][1];
-                if (!OCP && lane == 0) {
-                    s.child_out[0][0] = neg_tot;
-                    s.child_out[0][1] = pos_tot;
+        if (CL > 1) {
+            // this block's tallies go to the first block's sums (atomic adds into its shared memory), then start from zero
+            __syncthreads();
+            if (tid < 2 * A) {
+                const int v = s.tally[tid >> 1][tid & 1];
+                if (v != 0) {
+                    atomicAdd(&cg::this_cluster().map_shared_rank(&s, 0)->gather[tid >> 1][tid & 1], v);
+                    s.tally[tid >> 1][tid & 1] = 0;
                 }
             }
-            const int plen = s.path_len;
-            for (int e = lane; e < plen; e += 32) {
-                const int node = s.path[e];
-                const int turn_e = (e & 1) ? -s.root_turn : s.root_turn;
-                const int ns = s.path_ns[e] + (int)n_tot;
-                const int wins = s.path_wins[e] + (turn_e == 1 ? neg_tot : pos_tot);
-                if (e == plen - 1 && mode == MODE_ALL_CHILDREN) {
-                    rec[node] = make_int4(ns, wins, s.first_child, sel_meta | s.exp_mask);
-                } else {
-                    *reinterpret_cast<int2 *>(&rec[node]) = make_int2(ns, wins);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) {
-                s.out_neg = neg_tot;
-                s.out_pos = pos_tot;
-                s.stage_cycles[2] += c_backup - s.stage_mark;
-                s.stage_cycles[3] += (unsigned)clock() - c_backup;
-            }
-            __syncwarp();
+            cg::this_cluster().sync();
+        } else {
+            __syncthreads();
         }
     }
 
     // =============================================================== leave the per-tree state for the next launch
-    if (my_plies) atomicAdd(&s.plies, (unsigned long long)my_plies);
-    if (my_ub) {
-        atomicAdd(&s.ub, (unsigned long long)my_ub);
-        atomicOr(&s.status, STATUS_UB_DRAW);
+    {
+        Shared *home = CL > 1 ? cg::this_cluster().map_shared_rank(&s, 0) : &s;   // the first block keeps the tree's counters
+        if (my_plies) atomicAdd(&home->plies, (unsigned long long)my_plies);
+        if (my_ub) {
+            atomicAdd(&home->ub, (unsigned long long)my_ub);
+            atomicOr(&home->status, STATUS_UB_DRAW);
+        }
+        if (my_err) atomicOr(&home->status, STATUS_INTERNAL);
     }
-    if (my_err) atomicOr(&s.status, STATUS_INTERNAL);
-    __syncthreads();
-    for (int i = tid; i < n_streams; i += nt) g_rng[i] = s_rng[i];
+    if (CL > 1) cg::this_cluster().sync();   // also: no block leaves while another may still write to its shared memory
+    else __syncthreads();
+    for (int i = tid; i < (n_streams >> LOG_CL); i += nt)
+        g_rng[((i >> log2_local) << p.log2_playouts) + rank * P_local + (i & (P_local - 1))] = s_rng[i];
+    if (rank != 0) return;
     if (tid == 0) {
         st->size = s.size;
         st->selected = s.selected;
@@ -690,12 +766,8 @@ __device__ __forceinline__ long long global_timer_ns() {
     return t;
 }
 
-template <bool OCP>
-__global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
-    __shared__ Shared s;
-    extern __shared__ ulonglong2 s_rng[];
-    const int tid = threadIdx.x;
-    for (int i = tid; i < 128 * 8; i += blockDim.x) {
+__device__ __forceinline__ void build_move_lut(Shared &s) {
+    for (int i = threadIdx.x; i < 128 * 8; i += blockDim.x) {
         const int set = i >> 3, ord = i & 7;
         int col = -1, seen = 0;
         for (int c = 0; c < COLS; c++)
@@ -706,6 +778,17 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
         s.move_lut[i] = col < 0 ? MOVE_LUT_NO_COLUMN
                                 : (0x3FULL << (7 * col)) | ((unsigned long long)((1 << col) << LEGAL_SHIFT) << 48);
     }
+}
+
+#ifndef MCTSNC_C4_MAXNREG
+#define MCTSNC_C4_MAXNREG 64
+#endif
+template <bool OCP>
+__global__ void __maxnreg__(MCTSNC_C4_MAXNREG) search_kernel(const SearchParams p) {
+    __shared__ Shared s;
+    extern __shared__ ulonglong2 s_rng[];
+    const int tid = threadIdx.x;
+    build_move_lut(s);
     const bool queued = p.queue != nullptr;
     for (;;) {
         int g = blockIdx.x, rem = p.steps;
@@ -719,7 +802,7 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
         const int n_steps = (queued && rem > p.chunk) ? p.chunk : rem;
         long long t_start = 0;
         if (queued && tid == 0) t_start = global_timer_ns();
-        run_slice<OCP>(p, s, s_rng, g, n_steps, p.first != 0 && rem == p.steps);
+        run_slice<OCP, 1>(p, s, s_rng, g, n_steps, p.first != 0 && rem == p.steps);
         if (!queued) break;
         __syncthreads();  // every thread's writes of the slice precede the fence of thread 0
         if (tid == 0) {
@@ -754,6 +837,25 @@ __global__ void __maxnreg__(56) search_kernel(const SearchParams p) {
             }
         }
     }
+}
+
+// A cluster of CLUSTER_BLOCKS blocks per tree: launches with few trees (one search), where a step of a tree is bound by what one
+// SM can play.  Launched with the cluster dimension as a launch attribute; cluster c grows tree c for the whole launch.
+#ifndef MCTSNC_C4_CLUSTER_BLOCKS
+#define MCTSNC_C4_CLUSTER_BLOCKS 8
+#endif
+#ifndef MCTSNC_C4_CLUSTER_THREADS
+#define MCTSNC_C4_CLUSTER_THREADS 256
+#endif
+constexpr int CLUSTER_BLOCKS = MCTSNC_C4_CLUSTER_BLOCKS;
+constexpr int CLUSTER_THREADS = MCTSNC_C4_CLUSTER_THREADS;
+
+template <bool OCP>
+__global__ void __launch_bounds__(CLUSTER_THREADS) search_cluster_kernel(const SearchParams p) {
+    __shared__ Shared s;
+    extern __shared__ ulonglong2 s_rng[];
+    build_move_lut(s);
+    run_slice<OCP, CLUSTER_BLOCKS>(p, s, s_rng, (int)(blockIdx.x / CLUSTER_BLOCKS), p.steps, p.first != 0);
 }
 
 }  // namespace c4

@@ -32,6 +32,7 @@ constexpr int META_DEPTH_SHIFT = 16;
 constexpr int MODE_ALL_CHILDREN = -2;  // trees_actions_expanded[ti, -2] of the ACP variants
 constexpr int MODE_TERMINAL = -1;      // the selected node is terminal
 constexpr int MODE_TREE_FULL = -3;     // no room for any child
+constexpr int MODE_DONE = -4;          // inside a kernel: the steps of the launch are done
 
 constexpr unsigned STATUS_TREE_FULL = 1u;
 constexpr unsigned STATUS_UB_DRAW = 2u;
