@@ -66,7 +66,10 @@ typedef struct mctsnc_config {
        single-GPU search with n_trees_global trees (src/mctsnc.py:390-394, :1938, :2028). */
     int32_t tree_offset;
     int32_t n_trees_global;
-    int32_t threads_per_tree;   /* 0 = let the library choose; else threads of the block that grows one tree */
+    int32_t threads_per_tree;   /* 0 = let the library choose (Connect-4 launches with few trees of an ACP variant with 256
+                                   playouts or more then grow every tree with a cluster of 8 blocks; the environment
+                                   variable MCTSNC_B200_NO_CLUSTER=1, read at mctsnc_create, keeps one block per tree);
+                                   else threads of the one block that grows a tree */
     int32_t reserved;
 } mctsnc_config;
 
@@ -176,7 +179,8 @@ int mctsnc_export(mctsnc_handle *h, int32_t search, int32_t field, void *dst, in
    child-pick streams (one per tree).  For tests of the generator (numba create_xoroshiro128p_states). */
 int mctsnc_export_rng(mctsnc_handle *h, int32_t search, int32_t which, uint64_t *dst, int64_t n);
 
-/* Launch shape and memory the library chose (threads per tree, blocks resident per SM, bytes allocated). */
+/* Launch shape and memory the library chose (threads per tree -- all blocks of a tree's cluster together --, blocks
+   resident per SM, bytes allocated). */
 int mctsnc_query(mctsnc_handle *h, int32_t *threads_per_tree, int32_t *blocks_per_sm, int32_t *sm_count,
                  int64_t *bytes_allocated);
 
