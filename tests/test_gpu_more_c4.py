@@ -86,16 +86,17 @@ def test_two_shards_equal_the_unsharded_search(variant):
         assert np.array_equal(total_n, orc.field("actions_ns")) and np.array_equal(total_w, orc.field("actions_ns_wins"))
 
 
-def test_time_limited_search_is_a_prefix_of_the_step_limited_one():
+@pytest.mark.parametrize("n_playouts,time_limit", [(64, 0.02), (256, 0.01)])   # 256: a cluster of blocks per tree
+def test_time_limited_search_is_a_prefix_of_the_step_limited_one(n_playouts, time_limit):
     """A time budget runs the loop as several launches; the trees must equal those of one launch with as many steps."""
-    ai = MCTSNC((6, 7), 7, 7, search_time_limit=0.02, n_trees=2, n_playouts=64, variant="acp_prodigal", seed=2,
+    ai = MCTSNC((6, 7), 7, 7, search_time_limit=time_limit, n_trees=2, n_playouts=n_playouts, variant="acp_prodigal", seed=2,
                 verbose_info=False, node_capacity=200000)
     ai.init_device_side_arrays()
     board, fills = np.zeros((6, 7), np.int8), np.zeros(7, np.int8)
     best = ai.run(board, fills, 1)
     steps = ai.steps
     assert steps > 16          # more than one launch
-    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=2, n_playouts=64, variant="acp_prodigal", seed=2, node_capacity=steps * 7 + 8)
+    orc = OracleMCTSNC((6, 7), 7, 7, n_trees=2, n_playouts=n_playouts, variant="acp_prodigal", seed=2, node_capacity=steps * 7 + 8)
     orc.run(board, fills, 1, steps)
     compare_trees(ai, orc)
     assert int(best) == orc.best_action
@@ -103,6 +104,29 @@ def test_time_limited_search_is_a_prefix_of_the_step_limited_one():
     ai.reset_random_streams()
     ai.run(board, fills, 1, forced_search_steps_limit=25)
     assert ai.steps == 25
+
+
+def test_cluster_of_blocks_per_tree_equals_one_block_per_tree(monkeypatch):
+    """Launches with few trees of an ACP search with 256 playouts grow a tree with a cluster of 8 blocks; with the switch
+    in the environment, or a fixed number of threads, with one block: same trees, same streams afterwards."""
+    boards, fills, turns = c4_random_roots(3, 12, seed=21)
+    kw = dict(search_time_limit=np.inf, search_steps_limit=120, n_trees=3, n_playouts=256, variant="acp_thrifty", seed=9,
+              verbose_info=False, max_batch=3)
+    a = MCTSNC((6, 7), 7, 7, **kw)
+    a.init_device_side_arrays()
+    out_a = a.run_batch(boards, fills, turns, steps=120, reseed=True)
+    assert a.launch_geometry()["threads_per_tree"] == 2048
+    monkeypatch.setenv("MCTSNC_B200_NO_CLUSTER", "1")
+    b = MCTSNC((6, 7), 7, 7, **kw)
+    b.init_device_side_arrays()
+    out_b = b.run_batch(boards, fills, turns, steps=120, reseed=True)
+    assert b.launch_geometry()["threads_per_tree"] == 1024
+    for name in ("best_action", "best_n", "best_n_wins", "actions_ns", "actions_ns_wins", "playouts", "plies", "status"):
+        assert np.array_equal(out_a[name], out_b[name]), name
+    for search in range(3):
+        for field in ("trees_ns", "trees_ns_wins"):
+            assert np.array_equal(a.export(field, search=search), b.export(field, search=search))
+        assert np.array_equal(_streams(a, 0, 3 * 7 * 256, search), _streams(b, 0, 3 * 7 * 256, search))
 
 
 def test_info_dicts_have_the_reference_keys(capsys):
