@@ -656,6 +656,10 @@ constexpr int WARP_ACTIVE = TPL_WORDS, WARP_WORDS = TPL_WORDS + 60;
 constexpr size_t DYN_SMEM_BYTES = sizeof(unsigned) * ((size_t)THREAD_WORDS * DYN_THREADS + (size_t)WARP_WORDS * (DYN_THREADS / 32)) + FIVE_BYTES;
 static_assert((THREAD_WORDS * DYN_THREADS) % 4 == 0 && WARP_WORDS % 4 == 0 && TPL_LINES % 4 == 0, "16-byte loads of the warp's copy");
 
+// byte offset of list entry q of a thread from the thread's word 0: byte q & 3 of word q >> 2, words DYN_THREADS apart;
+// (q >> 2) * 4 * DYN_THREADS + (q & 3) written as one shift and one multiply-add
+__device__ __forceinline__ int list_byte(int q) { return (q >> 2) * (4 * DYN_THREADS - 4) + q; }
+
 template <bool OCP>
 __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Params p, int total_trees) {
     extern __shared__ __align__(16) unsigned s_mem[];
@@ -797,8 +801,8 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 {
                     const unsigned char *list = reinterpret_cast<const unsigned char *>(my);
                     const int q_last = max(count - 1, 0);
-                    next_last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
-                    next_cell = list[((ord >> 2) * DYN_THREADS) * 4 + (ord & 3)];
+                    next_last = list[list_byte(q_last)];
+                    next_cell = list[list_byte(ord)];
                 }
                 plies = 0;
                 playing = true;
@@ -844,12 +848,12 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
                 // ply are fetched, so that they arrive while this ply's stone is tested.
                 unsigned char *list = reinterpret_cast<unsigned char *>(my);
                 const int cell = next_cell;
-                list[((this_ord >> 2) * DYN_THREADS) * 4 + (this_ord & 3)] = (unsigned char)next_last;
+                list[list_byte(this_ord)] = (unsigned char)next_last;
                 count--;
                 count_2m64 -= RNG_2M64;   // exact: small integers times 2^-64
                 const int q_last = max(count - 1, 0);
-                next_last = list[((q_last >> 2) * DYN_THREADS) * 4 + (q_last & 3)];
-                next_cell = list[((ord >> 2) * DYN_THREADS) * 4 + (ord & 3)];   // ord <= count <= 225: inside the list words
+                next_last = list[list_byte(q_last)];
+                next_cell = list[list_byte(ord)];   // ord <= count <= 225: inside the list words
                 const int i = cell >> 4, j = cell & 15;
                 const int hs = turn > 0 ? 16 : 0;
                 plies++;

@@ -698,17 +698,17 @@ int launch_search_gomoku(mctsnc_handle *h, int batch, int steps, int first, cuda
             if (ocp) gomoku::tree_step_kernel<true><<<n, 256, 0, gs>>>(p);
             else gomoku::tree_step_kernel<false><<<n, 256, 0, gs>>>(p);
             if (s == steps) continue;
-            // Blocks of the launch.  Few trees (one search): a lane for every game of the step (OCP: one child per tree, ACP:
-            // up to 225 children) -- there are not enough games to keep the device busy anyway, and a step is as long as
-            // its longest chain of games.  Many trees: the group's share of the blocks that fit on the device at once (a
-            // quarter more, to cover groups that are between two playout launches), so that a lane plays several games one
-            // after the other and its warp stays full; with a lane for every game each warp would wait for the longest
-            // of its 32 games (mean ~85 plies, longest ~170).  Measured, 4 x 256 acp_prodigal: one search 132 ms per 500
-            // steps with a lane per game against 142 ms with shares; eight searches 904 ms with shares against 1014 ms.
+            // Blocks of the launch.  A lane for every game while that does not oversubscribe the device much (OCP: one child
+            // per tree); otherwise 1.5 to 2 times the group's share of the blocks that fit on the device at once, so that a
+            // lane plays several games one after the other and its warp stays full, and blocks are waiting to start
+            // where another group's launch is running out of games (a step is as long as its longest chain of games, mean
+            // ~85 plies, longest ~170).  Measured, 4 x 256 acp_prodigal, 500 steps, one search (4 groups) / eight searches
+            // (8 groups): 1.0 times the share 90.9 / 597 ms, 1.25: 86.4 / 541, 1.5: 85.3 / 525, 2: 87.7 / 515.
             const long long games = (long long)n * h->cfg.n_playouts * (ocp ? 1 : h->A);
             const long long enough = (games + gomoku::DYN_THREADS - 1) / gomoku::DYN_THREADS;
             long long blocks = enough;
-            if (enough * groups > (5 * resident) / 2) blocks = (5 * resident + 4 * groups - 1) / (4 * groups);
+            const long long quarters = groups >= GOMOKU_STREAMS ? 8 : 6;
+            if (enough * groups > (5 * resident) / 2) blocks = (quarters * resident + 4 * groups - 1) / (4 * groups);
             if (blocks > enough) blocks = enough;
             if (blocks > resident) blocks = resident;
             if (blocks < 1) blocks = 1;
