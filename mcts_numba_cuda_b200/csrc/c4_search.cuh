@@ -226,6 +226,21 @@ struct Shared {
     unsigned stage_mark;        // cycle counter when the playouts of the current step began
 };
 
+// Node records through the copy the walker keeps of a tree's first `cache_n` records (cluster kernel: the walk down the tree
+// is a chain of dependent loads, and the upper levels of a tree are its oldest nodes); cache_n = 0: global memory only.
+// Every store goes to both.
+__device__ __forceinline__ int4 rec_load(const int4 *rec, const int4 *cache, int cache_n, int i) {
+    return i < cache_n ? cache[i] : rec[i];
+}
+__device__ __forceinline__ void rec_store(int4 *rec, int4 *cache, int cache_n, int i, int4 v) {
+    rec[i] = v;
+    if (i < cache_n) cache[i] = v;
+}
+__device__ __forceinline__ void rec_store_stats(int4 *rec, int4 *cache, int cache_n, int i, int ns, int wins) {
+    *reinterpret_cast<int2 *>(&rec[i]) = make_int2(ns, wins);
+    if (i < cache_n) *reinterpret_cast<int2 *>(&cache[i]) = make_int2(ns, wins);
+}
+
 // `n_steps` steps of tree g by the whole block, from the state the tree has in global memory and back to it.
 // The random streams of the tree (ACP: 7*P, OCP: P states of 16 B) stay in dynamic shared memory meanwhile: they are
 // read at the start of every game and written back at its end, by one thread each.
@@ -237,9 +252,10 @@ struct Shared {
 // to the first block's `gather`.  Two cluster barriers per step; all blocks run the same loop, so every block reaches
 // every barrier.
 template <bool OCP, int CL>
-__device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulonglong2 *s_rng, const int g, const int n_steps,
-                                          const bool first) {
+__device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulonglong2 *s_rng, int4 *cache, const int g,
+                                          const int n_steps, const bool first) {
     namespace cg = cooperative_groups;
+    const int cache_n = CL > 1 ? p.cache_nodes : 0;
     static_assert(CL == 1 || CL == 2 || CL == 4 || CL == 8, "cluster sizes");
     constexpr int LOG_CL = CL == 8 ? 3 : (CL == 4 ? 2 : (CL == 2 ? 1 : 0));
     const int tid = threadIdx.x;
@@ -267,7 +283,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
         const int b = g / p.n_trees;
         if (first) {
             const int turn = p.root_turn[b];
-            rec[0] = make_int4(0, 0, -1, make_meta(0, false, 2, turn, 0));
+            rec_store(rec, cache, cache_n, 0, make_int4(0, 0, -1, make_meta(0, false, 2, turn, 0)));
             board[0] = p.root_board[b];
             parent[0] = -1;
             s.size = 1;
@@ -299,6 +315,11 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
     }
     if (CL > 1) cg::this_cluster().sync();
     else __syncthreads();
+    if (CL > 1 && rank == 0 && !first) {   // a search that goes on: the records the tree has so far
+        const int have = s.size < cache_n ? s.size : cache_n;
+        for (int i = tid; i < have; i += nt) cache[i] = rec[i];
+        __syncthreads();
+    }
 
     const double c_ucb = (double)p.ucb_c;
     unsigned my_plies = 0, my_ub = 0, my_err = 0;
@@ -339,8 +360,8 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                         // thread-0 part of _backup_ocp credit them (:2172-2177, :2104-2114)
                         const int cns = played ? P : 0;
                         const int cw = played ? (child_turn == 1 ? my_neg : my_pos) : 0;
-                        rec[s.first_child + lane] =
-                            make_int4(cns, cw, -1, make_meta(0, o != 2, o, child_turn, meta_depth(sel_meta) + 1));
+                        rec_store(rec, cache, cache_n, s.first_child + lane,
+                                  make_int4(cns, cw, -1, make_meta(0, o != 2, o, child_turn, meta_depth(sel_meta) + 1)));
                         if (!OCP) {
                             s.child_out[s.child_action[lane]][0] = my_neg;
                             s.child_out[s.child_action[lane]][1] = my_pos;
@@ -367,9 +388,9 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                     const int ns = s.path_ns[e] + (int)n_tot;
                     const int wins = s.path_wins[e] + (turn_e == 1 ? neg_tot : pos_tot);
                     if (e == plen - 1 && mode == MODE_ALL_CHILDREN) {
-                        rec[node] = make_int4(ns, wins, s.first_child, sel_meta | s.exp_mask);
+                        rec_store(rec, cache, cache_n, node, make_int4(ns, wins, s.first_child, sel_meta | s.exp_mask));
                     } else {
-                        *reinterpret_cast<int2 *>(&rec[node]) = make_int2(ns, wins);
+                        rec_store_stats(rec, cache, cache_n, node, ns, wins);
                     }
                 }
                 __syncwarp();
@@ -389,7 +410,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
             }
             const unsigned c_step = (unsigned)clock();   // 32-bit cycle counts: differences are right modulo 2^32
             int node = 0;
-            int4 r = rec[0];
+            int4 r = rec_load(rec, cache, cache_n, 0);
             int depth = 0;
             if (lane == 0) {
                 s.path[0] = 0;
@@ -408,7 +429,7 @@ __device__ __forceinline__ void run_slice(const SearchParams &p, Shared &s, ulon
                 double log_child = 0.0;
                 if (lane < A && ((mask >> lane) & 1u)) {
                     child = r.z + __popc(mask & ((1u << lane) - 1u));
-                    cr = rec[child];
+                    cr = rec_load(rec, cache, cache_n, child);
                     float v;
                     if (cr.x == 0) {
                         v = __int_as_float(0x7f800000);
@@ -802,7 +823,7 @@ __global__ void __maxnreg__(MCTSNC_C4_MAXNREG) search_kernel(const SearchParams 
         const int n_steps = (queued && rem > p.chunk) ? p.chunk : rem;
         long long t_start = 0;
         if (queued && tid == 0) t_start = global_timer_ns();
-        run_slice<OCP, 1>(p, s, s_rng, g, n_steps, p.first != 0 && rem == p.steps);
+        run_slice<OCP, 1>(p, s, s_rng, nullptr, g, n_steps, p.first != 0 && rem == p.steps);
         if (!queued) break;
         __syncthreads();  // every thread's writes of the slice precede the fence of thread 0
         if (tid == 0) {
@@ -855,7 +876,9 @@ __global__ void __launch_bounds__(CLUSTER_THREADS) search_cluster_kernel(const S
     __shared__ Shared s;
     extern __shared__ ulonglong2 s_rng[];
     build_move_lut(s);
-    run_slice<OCP, CLUSTER_BLOCKS>(p, s, s_rng, (int)(blockIdx.x / CLUSTER_BLOCKS), p.steps, p.first != 0);
+    const int n_local = ((OCP ? 1 : A) * p.n_playouts) / CLUSTER_BLOCKS;   // streams this block keeps; the record cache follows
+    run_slice<OCP, CLUSTER_BLOCKS>(p, s, s_rng, reinterpret_cast<int4 *>(s_rng + n_local), (int)(blockIdx.x / CLUSTER_BLOCKS), p.steps,
+                                   p.first != 0);
 }
 
 }  // namespace c4

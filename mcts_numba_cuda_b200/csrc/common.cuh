@@ -205,6 +205,7 @@ struct SearchParams {
     int *trace_count;
     int trace_cap;
     float ms_per_cycle;      // 1 / (nominal SM clock in kHz): converts cycle counts into the stage times of TreeState
+    int cache_nodes;         // cluster kernel: node records of a tree (the first ones) kept in the first block's shared memory
 };
 
 }  // namespace mctsnc

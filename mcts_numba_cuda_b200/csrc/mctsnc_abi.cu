@@ -23,6 +23,9 @@ using namespace mctsnc;
 namespace {
 
 constexpr int MAX_TREE_DEPTH = 2048;  // src/mctsnc.py:197
+#ifndef MCTSNC_C4_CACHE_NODES
+#define MCTSNC_C4_CACHE_NODES 8192      // Connect-4 cluster kernel, one block per SM: node records kept in shared memory
+#endif
 #ifndef MCTSNC_C4_CLUSTER_SM_SHARE
 #define MCTSNC_C4_CLUSTER_SM_SHARE 4   // Connect 4: clusters of blocks per tree while they make at most this many blocks per SM
 #endif
@@ -67,6 +70,7 @@ struct mctsnc_handle {
     int tpb_roa = 0;
     int sm_count = 0;
     bool cluster_ok = false;      // thread-block clusters can be launched (and MCTSNC_B200_NO_CLUSTER is not set)
+    bool cluster_smem_set = false;
     int threads = 0;
     int blocks_per_sm = 0;
     long long bytes = 0;
@@ -749,6 +753,7 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
     p.first = first;
     p.ucb_c = h->cfg.ucb_c;
     p.ms_per_cycle = h->ms_per_cycle;
+    p.cache_nodes = 0;
     const long long trees = (long long)batch * h->cfg.n_trees;
     p.queue = nullptr;
     p.ring = nullptr;
@@ -769,7 +774,14 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3((unsigned)(trees * c4::CLUSTER_BLOCKS));
         lc.blockDim = dim3(c4::CLUSTER_THREADS);
-        lc.dynamicSmemBytes = h->dyn_smem / c4::CLUSTER_BLOCKS;
+        // the first records of a tree stay in the first block's shared memory: as many as fit next to the other blocks
+        p.cache_nodes = trees * c4::CLUSTER_BLOCKS <= h->sm_count ? MCTSNC_C4_CACHE_NODES : 2048;
+        lc.dynamicSmemBytes = h->dyn_smem / c4::CLUSTER_BLOCKS + sizeof(int4) * (size_t)p.cache_nodes;
+        if (!h->cluster_smem_set) {
+            cudaFuncSetAttribute(c4::search_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+            cudaFuncSetAttribute(c4::search_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+            h->cluster_smem_set = true;
+        }
         lc.stream = stream;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -1594,6 +1606,7 @@ extern "C" int mctsnc_search_c4_static(const int8_t *board, const int8_t *extra_
     p.trace_count = nullptr;
     p.trace_cap = 0;
     p.ms_per_cycle = 0.f;
+    p.cache_nodes = 0;
     const size_t dyn_smem = sizeof(ulonglong2) * (size_t)per_tree;   // <= 28 KB: below the 48 KB that need an opt-in
     if (ocp) c4::search_kernel<true><<<n_trees, 256, dyn_smem, s>>>(p);
     else c4::search_kernel<false><<<n_trees, 256, dyn_smem, s>>>(p);
