@@ -647,6 +647,10 @@ constexpr int REFILL_MIN = MCTSNC_GOMOKU_REFILL_MIN;
 #define MCTSNC_GOMOKU_PLIES_PER_LOOK 8
 #endif
 constexpr int PLIES_PER_LOOK = MCTSNC_GOMOKU_PLIES_PER_LOOK;   // plies between two looks at whether lanes are idle
+#ifndef MCTSNC_GOMOKU_UNROLL
+#define MCTSNC_GOMOKU_UNROLL 8
+#endif
+constexpr int PLY_COPIES = MCTSNC_GOMOKU_UNROLL;   // copies of the ply's code in the loop between two looks
 #ifndef MCTSNC_GOMOKU_THREADS
 #define MCTSNC_GOMOKU_THREADS 224
 #endif
@@ -820,7 +824,7 @@ __global__ void __launch_bounds__(DYN_THREADS) playout_dynamic_kernel(const Para
             }
             if (__ballot_sync(0xFFFFFFFFu, playing) == 0u) break;
         }
-#pragma unroll
+#pragma unroll(PLY_COPIES)
         for (int rep = 0; rep < PLIES_PER_LOOK; rep++) {
           if (playing) {
             // ---- one ply (src/mctsnc.py:2059-2064).  float32 u * int16 count -> float32 (:2061); here (u * 2^64) * (count * 2^-64):
