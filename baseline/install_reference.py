@@ -2,7 +2,7 @@
 committed) so that the reference itself can be run next to this library -- its CPU search ``MCTS`` as the timed CPU
 baseline, its numba.cuda ``MCTSNC`` as the GPU denominator, its ``GameRunner`` as the driver of the replay test.
 
-    python baseline/install_reference.py [<reference root>]        (default: $MCTS_REFERENCE_ROOT or /root/reference)
+    python baseline/install_reference.py [<reference root>]        (default: $MCTS_REFERENCE_ROOT, else where the reference is usually mounted)
 
 The reference has no ``setup.py`` / ``pyproject.toml``, so there is nothing for pip to install; its modules are plain
 files that import each other by name (``from mctsnc import MCTSNC``), i.e. they expect their directory on ``sys.path``.

@@ -88,31 +88,15 @@ __device__ __forceinline__ unsigned ordered_key(float v) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__device__ __forceinline__ bool has_stone(const unsigned *set, int i, int j) {
-    const int c = i * N + j;
-    return (set[c >> 5] >> (c & 31)) & 1u;
-}
-
-// compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) for a stone just placed at (i, j): a line of exactly
-// five through it (scans stop after 5 stones either way, so "total == 4" rejects longer lines)
-__device__ __forceinline__ bool exactly_five(const unsigned *mine, int i, int j) {
-    const int di[4] = {1, 0, 1, 1}, dj[4] = {0, 1, 1, -1};
-#pragma unroll
-    for (int d = 0; d < 4; d++) {
-        int total = 0;
-        for (int k = 1; k < 6; k++) {
-            const int ii = i + k * di[d], jj = j + k * dj[d];
-            if (ii < 0 || ii >= M || jj < 0 || jj >= N || !has_stone(mine, ii, jj)) break;
-            total++;
-        }
-        for (int k = 1; k < 6; k++) {
-            const int ii = i - k * di[d], jj = j - k * dj[d];
-            if (ii < 0 || ii >= M || jj < 0 || jj >= N || !has_stone(mine, ii, jj)) break;
-            total++;
-        }
-        if (total == 4) return true;
-    }
-    return false;
+// compute_outcome_gomoku (src/mctsnc_game_mechanics.py:220-272) for one direction, on a line word of the form the playouts
+// keep (see below): does the stone that `hs` (0: player -1, 16: player +1) puts at position `pos` make a line of exactly
+// five?  The reference counts at most 5 stones either way and wants a total of 4, i.e. a run of exactly five that holds
+// the stone; cells that do not exist are never set, so the ends of the board count as empty.
+__device__ __forceinline__ bool five_on_line(unsigned word, int hs, int pos) {
+    const unsigned u = ((word >> hs) & 0x7FFFu) | (1u << pos);
+    const unsigned f = u & (u >> 1) & (u >> 2) & (u >> 3) & (u >> 4);   // bit s: stones at s .. s + 4
+    const unsigned e = f & ~(u << 1) & ~(u >> 5);                        // and none at s - 1 and s + 5
+    return (e & ((0x1Fu << pos) >> 4)) != 0u;                            // runs that hold pos: s = pos - 4 .. pos
 }
 
 // block-wide max of a 32-bit key followed by min of a tie-break value among the threads that hold the max
@@ -168,6 +152,7 @@ constexpr int FIVE_BYTES = 2048;
 template <bool OCP>
 __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
     __shared__ unsigned s_board[16];
+    __shared__ unsigned s_lines[15 + 15 + 16 + 16];   // the selected node's stones by line (LINE_WORDS words, see below)
     __shared__ int s_prefix[9];      // empty cells before word w
     __shared__ unsigned s_red[8];
     __shared__ int s_red_i[2][8];
@@ -392,34 +377,38 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
                 if ((empty >> bit) & 1u)
                     tpl_list[s_prefix[w] + __popc(empty & ((1u << bit) - 1u))] = (unsigned char)(((tid / N) << 4) | (tid % N));
             }
-            if (tid < LINE_WORDS) {
-                const int family = tid < 15 ? 0 : (tid < 30 ? 1 : (tid < 46 ? 2 : 3));
-                const int idx = tid - (family == 0 ? 0 : (family == 1 ? 15 : (family == 2 ? 30 : 46)));
-                unsigned word = 0;
-                for (int pos = 0; pos < 15; pos++) {
-                    for (int fold = 0; fold < 2; fold++) {   // the two lines of a folded word; rows and columns have one
-                        int i, j;
-                        if (family == 0) {
-                            i = idx;
-                            j = pos;
-                        } else if (family == 1) {
-                            i = pos;
-                            j = idx;
-                        } else if (family == 2) {
-                            j = pos;
-                            i = idx + 16 * fold - 14 + j;
-                        } else {
-                            j = pos;
-                            i = idx + 16 * fold - j;
-                        }
-                        if ((family < 2 && fold == 1) || i < 0 || i >= M) continue;
-                        const int c = i * N + j;
-                        if ((s_board[c >> 5] >> (c & 31)) & 1u) word |= 1u << pos;
-                        if ((s_board[8 + (c >> 5)] >> (c & 31)) & 1u) word |= 1u << (16 + pos);
+            // the line words: one (line, position) pair per thread and round, the cell's stones OR-ed into the line's word
+            if (tid < LINE_WORDS) s_lines[tid] = 0u;
+            __syncthreads();
+            for (int pair = tid; pair < LINE_WORDS * 15; pair += 256) {
+                const int lt = pair / 15, pos = pair - lt * 15;
+                const int family = lt < 15 ? 0 : (lt < 30 ? 1 : (lt < 46 ? 2 : 3));
+                const int idx = lt - (family == 0 ? 0 : (family == 1 ? 15 : (family == 2 ? 30 : 46)));
+                unsigned bits = 0;
+                for (int fold = 0; fold < 2; fold++) {   // the two lines of a folded word; rows and columns have one
+                    int i, j;
+                    if (family == 0) {
+                        i = idx;
+                        j = pos;
+                    } else if (family == 1) {
+                        i = pos;
+                        j = idx;
+                    } else if (family == 2) {
+                        j = pos;
+                        i = idx + 16 * fold - 14 + j;
+                    } else {
+                        j = pos;
+                        i = idx + 16 * fold - j;
                     }
+                    if ((family < 2 && fold == 1) || i < 0 || i >= M) continue;
+                    const int c = i * N + j;
+                    if ((s_board[c >> 5] >> (c & 31)) & 1u) bits |= 1u << pos;
+                    if ((s_board[8 + (c >> 5)] >> (c & 31)) & 1u) bits |= 1u << (16 + pos);
                 }
-                tpl[TPL_LINES + tid] = word;
+                if (bits) atomicOr(&s_lines[lt], bits);
             }
+            __syncthreads();
+            if (tid < LINE_WORDS) tpl[TPL_LINES + tid] = s_lines[tid];
         }
         const int size = st->size;
         long long room = p.node_limit - (long long)size;
@@ -452,17 +441,16 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
                 const int rank = s_prefix[w] + __popc(empty & ((1u << bit) - 1u));
                 if (legal && rank < n_exp) {
                     // _expand_2_*: the child's position and outcome (:1794-1821)
-                    unsigned mine[WORDS];
-                    const int off = sel_turn > 0 ? 8 : 0;
-#pragma unroll
-                    for (int k = 0; k < WORDS; k++) mine[k] = s_board[off + k];
-                    mine[w] |= 1u << bit;
-                    const bool win = exactly_five(mine, tid / N, tid % N);
+                    const int off = sel_turn > 0 ? 8 : 0, hs = sel_turn > 0 ? 16 : 0;
+                    const int i = tid / N, j = tid - i * N;
+                    const bool win = five_on_line(s_lines[i], hs, j) || five_on_line(s_lines[15 + j], hs, i) ||
+                                     five_on_line(s_lines[30 + ((i - j + 14) & 15)], hs, j) ||
+                                     five_on_line(s_lines[46 + ((i + j) & 15)], hs, j);
                     const int outcome = win ? sel_turn : (n_legal == 1 ? 0 : 2);
                     unsigned *cb = board + (long long)(first_child + rank) * 16;
 #pragma unroll
                     for (int k = 0; k < WORDS; k++) {
-                        cb[off + k] = mine[k];
+                        cb[off + k] = s_board[off + k] | (k == w ? 1u << bit : 0u);
                         cb[(8 - off) + k] = s_board[(8 - off) + k];
                     }
                     parent[first_child + rank] = node;
