@@ -434,6 +434,8 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
                 }
                 __syncthreads();
             }
+            bool plays = false;   // this thread's child needs real playouts
+            int my_rank = 0;
             if (tid < A) {
                 const int w = tid >> 5, bit = tid & 31;
                 const unsigned empty = ~(s_board[w] | s_board[8 + w]);
@@ -447,11 +449,19 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
                                      five_on_line(s_lines[30 + ((i - j + 14) & 15)], hs, j) ||
                                      five_on_line(s_lines[46 + ((i + j) & 15)], hs, j);
                     const int outcome = win ? sel_turn : (n_legal == 1 ? 0 : 2);
-                    unsigned *cb = board + (long long)(first_child + rank) * 16;
+                    uint4 *cb = reinterpret_cast<uint4 *>(board + (long long)(first_child + rank) * 16);
 #pragma unroll
-                    for (int k = 0; k < WORDS; k++) {
-                        cb[off + k] = s_board[off + k] | (k == w ? 1u << bit : 0u);
-                        cb[(8 - off) + k] = s_board[(8 - off) + k];
+                    for (int q = 0; q < 4; q++) {   // the parent's 16 words, the new stone in word off + w
+                        uint4 v = make_uint4(s_board[4 * q], s_board[4 * q + 1], s_board[4 * q + 2], s_board[4 * q + 3]);
+                        if (((off + w) >> 2) == q) {
+                            const unsigned stone = 1u << bit;
+                            const int k = (off + w) & 3;
+                            v.x |= k == 0 ? stone : 0u;
+                            v.y |= k == 1 ? stone : 0u;
+                            v.z |= k == 2 ? stone : 0u;
+                            v.w |= k == 3 ? stone : 0u;
+                        }
+                        cb[q] = v;
                     }
                     parent[first_child + rank] = node;
                     child_action[rank] = (unsigned char)tid;
@@ -462,9 +472,20 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
                     }
                     if (thrifty) ae[rank] = (short)tid;
                     else ae[tid] = (short)tid;
+                    plays = outcome == 2 && (!OCP || rank == s_pick);
+                    my_rank = rank;
                 } else if (!thrifty) {
                     ae[tid] = -1;
                 }
+            }
+            // the ranks of the children that are played out, ascending: position = playing children of lower rank
+            const unsigned playing_lanes = __ballot_sync(0xFFFFFFFFu, plays);
+            if (lane == 0) s_red[warp] = (unsigned)__popc(playing_lanes);
+            __syncthreads();
+            if (plays) {
+                int before = __popc(playing_lanes & ((1u << lane) - 1u));
+                for (int wb = 0; wb < warp; wb++) before += (int)s_red[wb];
+                p.active_rank[g * A + before] = (unsigned char)my_rank;
             }
         } else {
             mode = MODE_TREE_FULL;
@@ -493,12 +514,10 @@ __global__ void __launch_bounds__(256) tree_step_kernel(const Params p) {
         si->path_len = depth + 1;
         si->pick = pick;
         int n_active = 0;
-        unsigned char *active = p.active_rank + g * A;
         if (mode == MODE_ALL_CHILDREN) {
-            for (int k = 0; k < n_exp; k++)
-                if (child_outcome[k] == 2 && (!OCP || k == pick)) active[n_active++] = (unsigned char)k;
+            for (int wb = 0; wb < 8; wb++) n_active += (int)s_red[wb];
         } else if (mode == MODE_TREE_FULL) {
-            active[0] = 0;
+            p.active_rank[g * A] = 0;
             n_active = 1;
         }
         si->n_active = n_active;
