@@ -562,6 +562,7 @@ def secondary_runs(args, device):
             out[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     attempt("c4_ocp_thrifty_1x32_200steps_64roots", lambda: timed_search("c4", "ocp_thrifty", 1, 32, 200, 64, 10, 5, device))
+    attempt("c4_ocp_prodigal_8x128_1000steps_256roots", lambda: timed_search("c4", "ocp_prodigal", 8, 128, 1000, 256, 20, 2, device))
     attempt("gomoku_acp_prodigal_4x256_500steps_1root", lambda: timed_search("gomoku", "acp_prodigal", 4, 256, 500, 1, 30, 2, device))
     attempt("gomoku_acp_prodigal_4x256_500steps_8roots", lambda: timed_search("gomoku", "acp_prodigal", 4, 256, 500, 8, 30, 1, device))
     attempt("single_search_c4_acp_prodigal_4x256_2000steps", lambda: timed_search("c4", "acp_prodigal", 4, 256, 2000, 1, 0, 3, device))
