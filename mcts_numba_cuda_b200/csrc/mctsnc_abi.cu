@@ -573,12 +573,14 @@ const void *search_kernel_ptr(const mctsnc_config &c) {
 
 // Threads of the block that grows one tree, from the games a step plays (n_playouts, times the children of a node for
 // the ACP variants) and from how many trees there are for the device.
-//   Many trees (at least two per SM): a quarter of the games, between 32 and 320.  Measured on 256 roots: headline ACP
+//   Many trees (at least two per SM): a quarter of the games, between 32 and 320; half of them when a step has at most 256
+//   games.  Measured on 256 roots: headline ACP
 //   4 x 256 (1792 games a step) 16.9 / 18.2 / 17.3 / 15.8 / 15.7 G playouts/s at 256 / 320 / 384 / 448 / 512 threads (three
 //   blocks per SM up to 384; a thread of a smaller block plays more games per step, so less of a step is spent waiting for
 //   its last games); OCP 8 trees x 1000 steps with 32 / 128 / 512 playouts: 4.2 / 8.2 / 17.7 G/s at 32 / 64 / 128 threads
 //   against 1.4 / 5.0 / 12.8 at 384 (small blocks put more trees on an SM, which hides the latency of the
-//   select/expand/backup warp).
+//   select/expand/backup warp); with 8 x 1000 steps and 64 / 128 / 256 / 512 playouts, threads = playouts / 4, / 2, / 1:
+//   - / 6.3 / 5.9, 8.3 / 8.6 / 7.7, 11.3 / 13.0 / 10.5, 18.6 / 15.7 / 10.7 G/s.
 //   Few trees (a tree has an SM to itself): one thread per game, at most 1024; measured on one 4-tree ACP search of
 //   2000 steps: 94.7 ms with 256 threads, 69.3 ms with 512, 67.5 ms with 1024.  In between: half the games, at most 512.
 int choose_threads(mctsnc_handle *h, long long trees) {
@@ -588,7 +590,7 @@ int choose_threads(mctsnc_handle *h, long long trees) {
         return t < 32 ? 32 : (t > most ? most : t);
     };
     int threads;
-    if (trees >= 2LL * h->sm_count) threads = fit(games / 4, 320);
+    if (trees >= 2LL * h->sm_count) threads = fit(games <= 256 ? games / 2 : games / 4, 320);
     else if (trees <= h->sm_count) threads = fit(games, 1024);
     else threads = fit(games / 2, 512);
     const void *fn = search_kernel_ptr(h->cfg);

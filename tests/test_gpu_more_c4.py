@@ -335,6 +335,7 @@ def test_queued_batch_matches_oracle(variant):
     ("acp_prodigal", 4, 256, 128, 320),     # many trees, 1792 games a step: a quarter of the games, capped
     ("ocp_prodigal", 8, 32, 64, 32),        # many trees, 32 games a step: one warp
     ("ocp_prodigal", 8, 512, 64, 128),
+    ("ocp_prodigal", 8, 256, 64, 128),      # at most 256 games a step: half of them
     ("acp_prodigal", 4, 256, 1, 2048),      # few trees, more games a step than a block has threads: 8 blocks of 256 per tree
     ("acp_prodigal", 4, 128, 1, 896),       # a tree has an SM to itself: one thread per game
     ("ocp_thrifty", 1, 32, 1, 32),
