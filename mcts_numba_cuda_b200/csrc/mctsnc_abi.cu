@@ -71,6 +71,7 @@ struct mctsnc_handle {
     int sm_count = 0;
     bool cluster_ok = false;      // thread-block clusters can be launched (and MCTSNC_B200_NO_CLUSTER is not set)
     bool cluster_smem_set = false;
+    int cluster_fit[2] = {0, 0};  // clusters that fit on the device at once, by record-cache size (0: not asked yet, -1: unknown)
     int threads = 0;
     int blocks_per_sm = 0;
     long long bytes = 0;
@@ -776,14 +777,6 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3((unsigned)(trees * c4::CLUSTER_BLOCKS));
         lc.blockDim = dim3(c4::CLUSTER_THREADS);
-        // the first records of a tree stay in the first block's shared memory: as many as fit next to the other blocks
-        p.cache_nodes = trees * c4::CLUSTER_BLOCKS <= h->sm_count ? MCTSNC_C4_CACHE_NODES : 2048;
-        lc.dynamicSmemBytes = h->dyn_smem / c4::CLUSTER_BLOCKS + sizeof(int4) * (size_t)p.cache_nodes;
-        if (!h->cluster_smem_set) {
-            cudaFuncSetAttribute(c4::search_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
-            cudaFuncSetAttribute(c4::search_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
-            h->cluster_smem_set = true;
-        }
         lc.stream = stream;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -792,13 +785,38 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
         attr.val.clusterDim.z = 1;
         lc.attrs = &attr;
         lc.numAttrs = 1;
-        h->threads = c4::CLUSTER_THREADS * c4::CLUSTER_BLOCKS;
-        h->blocks_per_sm = 1;
-        const cudaError_t e = is_ocp(h->cfg) ? cudaLaunchKernelEx(&lc, c4::search_cluster_kernel<true>, p)
-                                             : cudaLaunchKernelEx(&lc, c4::search_cluster_kernel<false>, p);
-        if (e == cudaSuccess) return 0;
-        cudaGetLastError();      // the launch was refused (nothing ran): one block per tree from now on
-        h->cluster_ok = false;
+        if (!h->cluster_smem_set) {
+            cudaFuncSetAttribute(c4::search_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+            cudaFuncSetAttribute(c4::search_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+            h->cluster_smem_set = true;
+        }
+        // The first records of a tree stay in the first block's shared memory: many if every block can have an SM to itself,
+        // else few.  All clusters of the launch have to be on the device at once (clusters do not spread over GPCs, so fewer
+        // fit than blocks / 8): a tree whose cluster waits for another to finish would take two searches' time.
+        bool fits = false;
+        for (int small = trees * c4::CLUSTER_BLOCKS <= h->sm_count ? 0 : 1; small < 2 && !fits; small++) {
+            p.cache_nodes = small ? 2048 : MCTSNC_C4_CACHE_NODES;
+            lc.dynamicSmemBytes = h->dyn_smem / c4::CLUSTER_BLOCKS + sizeof(int4) * (size_t)p.cache_nodes;
+            int &fit = h->cluster_fit[small];
+            if (fit == 0) {
+                int n = 0;
+                const cudaError_t q = is_ocp(h->cfg) ? cudaOccupancyMaxActiveClusters(&n, c4::search_cluster_kernel<true>, &lc)
+                                                     : cudaOccupancyMaxActiveClusters(&n, c4::search_cluster_kernel<false>, &lc);
+                if (q != cudaSuccess) cudaGetLastError();
+                fit = q == cudaSuccess && n > 0 ? n : -1;
+            }
+            fits = fit >= trees;
+        }
+        if (fits) {
+            h->threads = c4::CLUSTER_THREADS * c4::CLUSTER_BLOCKS;
+            h->blocks_per_sm = 1;
+            const cudaError_t e = is_ocp(h->cfg) ? cudaLaunchKernelEx(&lc, c4::search_cluster_kernel<true>, p)
+                                                 : cudaLaunchKernelEx(&lc, c4::search_cluster_kernel<false>, p);
+            if (e == cudaSuccess) return 0;
+            cudaGetLastError();      // the launch was refused (nothing ran): one block per tree from now on
+            h->cluster_ok = false;
+        }
+        p.cache_nodes = 0;
     }
     const int threads = h->cfg.threads_per_tree > 0 ? h->cfg.threads_per_tree : choose_threads(h, trees);
     h->threads = threads;
