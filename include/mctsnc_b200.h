@@ -66,8 +66,8 @@ typedef struct mctsnc_config {
        single-GPU search with n_trees_global trees (src/mctsnc.py:390-394, :1938, :2028). */
     int32_t tree_offset;
     int32_t n_trees_global;
-    int32_t threads_per_tree;   /* 0 = let the library choose (Connect-4 launches with few trees of an ACP variant with 256
-                                   playouts or more then grow every tree with a cluster of 8 blocks; the environment
+    int32_t threads_per_tree;   /* 0 = let the library choose (Connect-4 launches with few trees and more than 256 games
+                                   a step then grow every tree with a cluster of 8 blocks; the environment
                                    variable MCTSNC_B200_NO_CLUSTER=1, read at mctsnc_create, keeps one block per tree);
                                    else threads of the one block that grows a tree */
     int32_t reserved;

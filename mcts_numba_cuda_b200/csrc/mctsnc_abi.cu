@@ -23,6 +23,9 @@ using namespace mctsnc;
 namespace {
 
 constexpr int MAX_TREE_DEPTH = 2048;  // src/mctsnc.py:197
+#ifndef MCTSNC_C4_CLUSTER_MIN_GAMES
+#define MCTSNC_C4_CLUSTER_MIN_GAMES 256    // Connect 4: clusters only for steps with more games than this
+#endif
 #ifndef MCTSNC_C4_CACHE_NODES
 #define MCTSNC_C4_CACHE_NODES 8192      // Connect-4 cluster kernel, one block per SM: node records kept in shared memory
 #endif
@@ -770,9 +773,12 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
     // several SMs at once.  Measured, 4 x 256 acp_prodigal, 2000 steps, 4 / 8 / 16 / 32 searches in one launch: 31.4 / 37.2 /
     // 40.4 / 63.2 ms with clusters against 57.3 / 57.3 / 57.3 / 57.4 ms with a block of 1024 threads per tree -- up to four
     // cluster blocks per SM pay.
-    // Only where a step has more games than a block has threads (ACP with 256 playouts or more): with a thread per game the
-    // step is as long as its longest game wherever the games are played, and the two cluster barriers of a step only cost.
-    if (h->cfg.threads_per_tree == 0 && h->cluster_ok && !is_ocp(h->cfg) && (long long)h->A * h->cfg.n_playouts > 1024 &&
+    // Only where a step has more than 256 games (ACP with 64 playouts or more, OCP with 512).  One search of 2000 steps, 4
+    // trees, with a block / with clusters: ACP 8 / 16 / 32 / 64 / 128 / 256 / 512 playouts 19.6 / 20.2 / 22.8 / 27.6 / 38.1 /
+    // 57.2 / - ms against 20.7 / 22.0 / 23.5 / 24.2 / 25.0 / 28.3 / 36.3 ms; OCP 32 / 128 / 512 playouts 19.8 / 20.7 / 28.9
+    // against 20.7 / 23.4 / 25.3 ms: with few games the two cluster barriers of a step cost more than the games take.
+    if (h->cfg.threads_per_tree == 0 && h->cluster_ok && h->cfg.n_playouts >= c4::CLUSTER_BLOCKS &&
+        (long long)(is_ocp(h->cfg) ? 1 : h->A) * h->cfg.n_playouts > MCTSNC_C4_CLUSTER_MIN_GAMES &&
         trees * c4::CLUSTER_BLOCKS <= (long long)MCTSNC_C4_CLUSTER_SM_SHARE * h->sm_count) {
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3((unsigned)(trees * c4::CLUSTER_BLOCKS));

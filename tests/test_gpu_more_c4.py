@@ -336,8 +336,9 @@ def test_queued_batch_matches_oracle(variant):
     ("ocp_prodigal", 8, 32, 64, 32),        # many trees, 32 games a step: one warp
     ("ocp_prodigal", 8, 512, 64, 128),
     ("ocp_prodigal", 8, 256, 64, 128),      # at most 256 games a step: half of them
-    ("acp_prodigal", 4, 256, 1, 2048),      # few trees, more games a step than a block has threads: 8 blocks of 256 per tree
-    ("acp_prodigal", 4, 128, 1, 896),       # a tree has an SM to itself: one thread per game
+    ("acp_prodigal", 4, 256, 1, 2048),      # few trees, more than 256 games a step: 8 blocks of 256 per tree
+    ("acp_prodigal", 4, 64, 1, 2048),
+    ("acp_prodigal", 4, 32, 1, 224),        # few games a step: a block per tree, one thread per game
     ("ocp_thrifty", 1, 32, 1, 32),
 ])
 def test_block_size_follows_the_games_per_step(variant, n_trees, n_playouts, roots, threads):
