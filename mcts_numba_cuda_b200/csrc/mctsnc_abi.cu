@@ -73,7 +73,6 @@ struct mctsnc_handle {
     int tpb_roa = 0;
     int sm_count = 0;
     bool cluster_ok = false;      // thread-block clusters can be launched (and MCTSNC_B200_NO_CLUSTER is not set)
-    bool cluster_smem_set = false;
     int cluster_fit[2] = {0, 0};  // clusters that fit on the device at once, by record-cache size (0: not asked yet, -1: unknown)
     int threads = 0;
     int blocks_per_sm = 0;
@@ -791,11 +790,8 @@ int launch_search(mctsnc_handle *h, int batch, int steps, int first, cudaStream_
         attr.val.clusterDim.z = 1;
         lc.attrs = &attr;
         lc.numAttrs = 1;
-        if (!h->cluster_smem_set) {
-            cudaFuncSetAttribute(c4::search_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
-            cudaFuncSetAttribute(c4::search_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
-            h->cluster_smem_set = true;
-        }
+        if (is_ocp(h->cfg)) cudaFuncSetAttribute(c4::search_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+        else cudaFuncSetAttribute(c4::search_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
         // The first records of a tree stay in the first block's shared memory: many if every block can have an SM to itself,
         // else few.  All clusters of the launch have to be on the device at once (clusters do not spread over GPCs, so fewer
         // fit than blocks / 8): a tree whose cluster waits for another to finish would take two searches' time.
@@ -988,7 +984,11 @@ extern "C" int mctsnc_create(const mctsnc_config *cfg, mctsnc_handle **out) {
     if (h->dyn_smem > 48 * 1024) {
         const void *kernel = is_gomoku(c) ? (ocp ? (const void *)gomoku::playout_dynamic_kernel<true> : (const void *)gomoku::playout_dynamic_kernel<false>)
                                           : search_kernel_ptr(c);
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
+        // the limit belongs to the kernel, not to the handle: never lower what another handle (or a launch) has asked for
+        cudaFuncAttributes now;
+        cudaError_t e = cudaFuncGetAttributes(&now, kernel);
+        if (e == cudaSuccess && (size_t)now.maxDynamicSharedSizeBytes < h->dyn_smem)
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h->dyn_smem);
         if (e != cudaSuccess) {
             delete h;
             return (int)e;
