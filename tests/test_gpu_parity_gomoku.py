@@ -75,13 +75,13 @@ def test_gomoku_random_roots_match_oracle(variant):
         assert int(best) == orc.best_action
 
 
-@pytest.mark.parametrize("variant,root_index", [("acp_prodigal", 0), ("acp_thrifty", 1)])
-def test_gomoku_headline_shape_4_trees_256_playouts_matches_oracle(variant, root_index):
+@pytest.mark.parametrize("variant,root_index,steps", [("acp_prodigal", 0, 8), ("acp_thrifty", 1, 8), ("acp_prodigal", 1, 40)])
+def test_gomoku_headline_shape_4_trees_256_playouts_matches_oracle(variant, root_index, steps):
     """The launch shape of BASELINE's Gomoku configuration (4 trees x 256 playouts, device_memory 16 GiB): up to 225
     children x 256 games per tree and step through the persistent playout grid, compared with the oracle field by field
-    after 8 steps.  The oracle searches run on host threads meanwhile (the ctypes calls release the interpreter lock)."""
+    after 8 steps, and after 40 (trees three levels deep, 9 000 nodes each, 2 M playouts).  The oracle searches run on host
+    threads meanwhile (the ctypes calls release the interpreter lock)."""
     from concurrent.futures import ThreadPoolExecutor
-    steps = 8
     boards, turns = gomoku_random_roots(2, 30, seed=11)
     board, turn = boards[root_index], int(turns[root_index])
     ai, orc = make_pair(variant, 4, 256, steps, seed=0)
