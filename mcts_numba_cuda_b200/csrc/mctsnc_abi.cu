@@ -27,7 +27,7 @@ constexpr int MAX_TREE_DEPTH = 2048;  // src/mctsnc.py:197
 #define MCTSNC_C4_CLUSTER_MIN_GAMES 256    // Connect 4: clusters only for steps with more games than this
 #endif
 #ifndef MCTSNC_C4_CACHE_NODES
-#define MCTSNC_C4_CACHE_NODES 8192      // Connect-4 cluster kernel, one block per SM: node records kept in shared memory
+#define MCTSNC_C4_CACHE_NODES 6144      // Connect-4 cluster kernel, one block per SM: node records kept in shared memory
 #endif
 #ifndef MCTSNC_C4_CLUSTER_SM_SHARE
 #define MCTSNC_C4_CLUSTER_SM_SHARE 4   // Connect 4: clusters of blocks per tree while they make at most this many blocks per SM
